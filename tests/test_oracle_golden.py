@@ -1,0 +1,112 @@
+"""Pin the CPU oracle against outputs of the reference itself (tests/golden/*.npz)."""
+from __future__ import annotations
+
+import torch
+
+from conftest import load_golden, regen_attention_layer
+from oracle import mimi_attention_oracle as O
+
+TOL = 2e-6   # FP32 reassociation noise between the oracle's eager softmax and the reference's SDPA
+
+
+def test_pairs_match_published_counts():
+    assert (O.pairs(125), O.pairs(250), O.pairs(2500)) == (7875, 31375, 593875)
+
+
+def test_rope_tables_and_isolated_op_match_reference():
+    g = load_golden("isolated_T250.npz")
+    gen = torch.Generator().manual_seed(int(g["seed"]))
+    q, k, v = (torch.randn(1, 8, 250, 64, generator=gen) / 8 for _ in range(3))
+    assert torch.equal(q[0, 0, :4], g["q_head0"]) and torch.equal(v[0, 7, -4:], g["v_head7"])
+    cos, sin = O.rope_tables(torch.arange(250))
+    rows = g["rows"]
+    assert torch.equal(cos[rows], g["cos"]) and torch.equal(sin[rows], g["sin"])
+    qr, kr = O.apply_rope(q, k, cos, sin)
+    assert torch.equal(qr[0][:, rows], g["q_rot"])
+    out = O.band_attention(qr, kr, v)
+    assert (out[0][:, rows] - g["out"]).abs().max() < TOL
+    out2 = O.band_attention_sdpa(qr, kr, v)
+    assert (out2[0][:, rows] - g["out"]).abs().max() < TOL
+
+
+def test_long_band_matches_reference():
+    g = load_golden("band_T700.npz")
+    gen = torch.Generator().manual_seed(int(g["seed"]))
+    q, k, v = (torch.randn(1, 8, 700, 64, generator=gen) / 8 for _ in range(3))
+    cos, sin = O.rope_tables(torch.arange(700))
+    qr, kr = O.apply_rope(q, k, cos, sin)
+    out = O.band_attention(qr, kr, v)
+    assert (out[0][:, g["rows"]] - g["out"]).abs().max() < TOL
+
+
+def test_tiny_attention_layer_matches_reference():
+    g = load_golden("tiny_attention_layer.npz")
+    out = O.attention_forward(g["x"], g["wq"], g["wk"], g["wv"], g["wo"], window=8, num_heads=2)
+    assert (out - g["out"]).abs().max() < TOL
+
+
+def test_full_size_attention_layers_match_reference():
+    for name in ("attention_layer_T250.npz", "attention_layer_T313.npz"):
+        g = load_golden(name)
+        x, wq, wk, wv, wo = regen_attention_layer(int(g["seed"]), int(g["b"]), int(g["t"]))
+        assert torch.equal(x[0, :2, :8], g["x_probe"]) and torch.equal(wq[:2, :8], g["wq_probe"])
+        out = O.attention_forward(x, wq, wk, wv, wo)
+        assert (out[:, g["rows"]] - g["out"]).abs().max() < TOL
+
+
+def _run_cached(g, window, heads):
+    cache = O.KVCacheOracle(window=window)
+    outs = []
+    for i, t in enumerate(g["chunks"].tolist()):
+        outs.append(O.attention_forward(g[f"x{i}"], g["wq"], g["wk"], g["wv"], g["wo"], cache=cache,
+                                        window=window, num_heads=heads))
+        assert cache.get_seq_length() == int(g["seq_lengths"][i])
+    return cache, outs
+
+
+def test_tiny_cached_chunks_and_decode_match_reference():
+    for name in ("tiny_cached_chunks.npz", "tiny_cached_decode.npz"):
+        g = load_golden(name)
+        cache, outs = _run_cached(g, 8, 2)
+        for i, out in enumerate(outs):
+            assert (out - g[f"out{i}"]).abs().max() < TOL, (name, i)
+        assert cache.keys[0].shape[-2] == 7
+        assert (cache.keys[0] - g["final_key_cache"]).abs().max() < TOL
+        assert (cache.values[0] - g["final_value_cache"]).abs().max() < TOL
+
+
+def test_ring_decode_260_matches_reference():
+    g = load_golden("ring_decode_260.npz")
+    torch.manual_seed(int(g["seed"]))
+    lins = [torch.nn.Linear(512, 512, bias=False) for _ in range(4)]
+    for lin in lins:
+        torch.nn.init.normal_(lin.weight, std=0.02)
+    wq, wk, wv, wo = (lin.weight.detach() for lin in lins)
+    cache = O.KVCacheOracle()
+    keep = g["keep_steps"].tolist()
+    got = []
+    for step in range(260):
+        x = torch.randn(2, 1, 512)
+        out = O.attention_forward(x, wq, wk, wv, wo, cache=cache)
+        if step in keep:
+            got.append(out)
+    assert cache.get_seq_length() == 260 and cache.keys[0].shape[-2] == 249
+    assert (torch.stack(got) - g["outs"]).abs().max() < TOL
+    assert (cache.keys[0][:, :, -3:] - g["final_key_cache"]).abs().max() < TOL
+
+
+def test_tiny_stack_prefill_and_chunked_match_reference():
+    g = load_golden("tiny_stack.npz")
+    params = {k[2:]: v for k, v in g.items() if k.startswith("p.")}
+
+    def run(x, cache):
+        past = cache.get_seq_length(0) if cache is not None else 0
+        for layer in range(2):
+            p = {k[len(f"layers.{layer}."):]: v for k, v in params.items() if k.startswith(f"layers.{layer}.")}
+            x = O.transformer_layer(x, p, cache=cache, layer=layer, window=8, num_heads=2, past_length=past)
+        return x
+
+    assert (run(g["x"], None) - g["full"]).abs().max() < TOL
+    cache = O.KVCacheOracle(window=8)
+    outs = [run(g["x"][:, a:b], cache) for a, b in ((0, 5), (5, 6), (6, 13), (13, 14), (14, 21))]
+    assert (torch.cat(outs, 1) - g["chunked"]).abs().max() < TOL
