@@ -1,0 +1,157 @@
+// extern "C" entry points of libfast_mimi_b200.so (declared in include/fast_mimi_b200.h) and the
+// small host helpers they share.  No torch types, no allocation, no synchronisation except
+// fm_read_status.
+#include "../../include/fast_mimi_b200.h"
+
+#include <mutex>
+
+#include "fm_kernels.h"
+
+namespace fm {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, void* base, const cuuint64_t* dims,
+                 const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* elem_strides,
+                 CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -4;
+  const CUresult r = fn(map, dtype, rank, base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return static_cast<int>(r);
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+  // cudaFuncSetAttribute is per device; remember which (kernel, device) pairs are done.
+  constexpr int kMaxDev = 64, kMaxKern = 16;
+  static std::mutex mu;
+  static const void* kerns[kMaxKern];
+  static bool done[kMaxKern][kMaxDev];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  std::lock_guard<std::mutex> lock(mu);
+  int slot = -1;
+  for (int i = 0; i < kMaxKern; ++i) {
+    if (kerns[i] == kernel) { slot = i; break; }
+    if (kerns[i] == nullptr) { kerns[i] = kernel; slot = i; break; }
+  }
+  if (slot >= 0 && dev < kMaxDev && done[slot][dev]) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (slot >= 0 && dev < kMaxDev) done[slot][dev] = true;
+  return 0;
+}
+
+}  // namespace fm
+
+using fm::QkvEpilogueArgs;
+
+extern "C" {
+
+int fm_abi_version(void) { return 1; }
+
+int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                     void* q, void* k, void* v, int B, int T, int value_dtype, int* status, void* stream) {
+  if (B < 0 || T < 0 || (value_dtype != 0 && value_dtype != 1)) return -1;
+  if (static_cast<long long>(B) * T > 0x7fffffffLL) return -1;
+  QkvEpilogueArgs ep = {};
+  ep.q = static_cast<uint16_t*>(q);
+  ep.k = static_cast<uint16_t*>(k);
+  ep.v = static_cast<uint16_t*>(v);
+  ep.cos = cos;
+  ep.sin = sin;
+  ep.cos_bstride = cos_bstride;
+  ep.T = T;
+  ep.ring_slots = 1;
+  return fm::launch_qkv_rope_gemm(x, w_qkv, ep, B * T, value_dtype, status, static_cast<cudaStream_t>(stream));
+}
+
+int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
+                              float scale, int value_dtype, int* status, void* stream) {
+  if (value_dtype != 0 && value_dtype != 1) return -1;
+  return fm::launch_band_attn_prefill(q, k, v, out, B, T, window, scale, value_dtype, status,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
+                              long long cos_bstride, void* q_ws, void* k_ws, void* v_ws, void* out, int B, int T,
+                              int window, float scale, int value_dtype, int* status, void* stream) {
+  int rc = fm_qkv_rope_bf16(x, w_qkv, cos, sin, cos_bstride, q_ws, k_ws, v_ws, B, T, value_dtype, status, stream);
+  if (rc != 0) return rc;
+  return fm_band_attn_prefill_bf16(q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype, status, stream);
+}
+
+int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring_v, float* out,
+                             const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
+                             int value_dtype, int* status, void* stream) {
+  if (value_dtype != 0 && value_dtype != 1) return -1;
+  return fm::launch_ring_decode_attn(q, ring_k, ring_v, out, stream_pos, pos_base, S, ring_slots, scale,
+                                     value_dtype, status, static_cast<cudaStream_t>(stream));
+}
+
+int fm_decode_step_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                        const int* stream_pos, int pos_base, void* q_ws, void* ring_k, void* ring_v, float* out,
+                        int S, int ring_slots, float scale, int value_dtype, int* status, void* stream) {
+  if (S < 0 || (value_dtype != 0 && value_dtype != 1) || ring_slots <= 0 || ring_slots > 256) return -1;
+  if (ring_k == nullptr || ring_v == nullptr || q_ws == nullptr) return -1;
+  QkvEpilogueArgs ep = {};
+  ep.q = static_cast<uint16_t*>(q_ws);
+  ep.ring_k = static_cast<uint16_t*>(ring_k);
+  ep.ring_v = static_cast<uint16_t*>(ring_v);
+  ep.cos = cos;
+  ep.sin = sin;
+  ep.cos_bstride = cos_bstride;
+  ep.clip_pos = stream_pos;
+  ep.pos_base = pos_base;
+  ep.T = 1;
+  ep.ring_slots = ring_slots;
+  int rc = fm::launch_qkv_rope_gemm(x, w_qkv, ep, S, value_dtype, status, static_cast<cudaStream_t>(stream));
+  if (rc != 0) return rc;
+  return fm::launch_ring_decode_attn(q_ws, ring_k, ring_v, out, stream_pos, pos_base, S, ring_slots, scale,
+                                     value_dtype, status, static_cast<cudaStream_t>(stream));
+}
+
+int fm_band_attn_fp32_verify(const float* q, const float* k, const float* v, float* out, int B, int H, int D, int Tq,
+                             int Tk, int q_off, int k_off, int window, float scale, const long long* strides,
+                             void* stream) {
+  if (strides == nullptr) return -1;
+  return fm::launch_band_attn_fp32(q, k, v, out, B, H, D, Tq, Tk, q_off, k_off, window, scale, strides,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int fm_linear_fp32_verify(const float* x, const float* w, float* y, int M, int N, int K, void* stream) {
+  return fm::launch_linear_fp32(x, w, y, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+int fm_rope_fp32_verify(float* t, const float* cos, const float* sin, int B, int T, int H, int D,
+                        long long cos_bstride, void* stream) {
+  return fm::launch_rope_fp32(t, cos, sin, B, T, H, D, cos_bstride, static_cast<cudaStream_t>(stream));
+}
+
+int fm_read_status(const int* status, void* stream) {
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (status == nullptr) return 0;
+  int host = 0;
+  e = cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return host;
+}
+
+}  // extern "C"

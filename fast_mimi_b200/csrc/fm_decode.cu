@@ -1,0 +1,217 @@
+// Single-frame streaming decode over a per-stream KV ring (HBM-bound) for sm_100a.
+//
+//   out[s, h, :] = softmax_j( scale * q[s,h,:] . K_ring[s,h,j,:] ) V_ring[s,h,j,:]   over the valid slots
+//
+// Replaces the cached one-frame attention of the reference: MimiKVCache.update's concat-and-crop
+// (src/fast_mimi/model.py:450-471) followed by SDPA with one query (src/fast_mimi/model.py:1860-1868).
+// The reference keeps the last window-1 rotated K/V rows and concatenates the new row; here the ring
+// has `window` slots, the projection epilogue has already written the new row into slot pos % window,
+// and softmax does not depend on slot order, so the visible set is identical.
+//
+// Work item = (stream, head): 2 x slots x 128 B of ring (K then V).  A persistent CTA streams items
+// through a 3-stage shared-memory ring with untiled TMA bulk copies issued by one producer thread
+// (192 KB in flight per SM); four consumer warps each take 64 slots: 16-byte vector reads, FP32
+// dot products, warp-shuffle reductions, and a four-way merge of (max, sum, output) through shared
+// memory.
+#include "fm_common.cuh"
+#include "fm_kernels.h"
+
+namespace fm {
+
+namespace dec {
+constexpr int kMaxSlots = 256;
+constexpr int kStages = 3;
+constexpr int kWarps = 4;
+constexpr int kThreads = (kWarps + 1) * 32;
+constexpr int kRowBytes = 128;
+
+struct Ctl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  CtaCtl ctl;
+  float merge_m[2][kWarps];
+  float merge_l[2][kWarps];
+  float merge_o[2][kWarps][64];
+};
+}  // namespace dec
+
+template <typename VT>
+__global__ void __launch_bounds__(dec::kThreads, 1)
+ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ ring_k,
+                        const uint16_t* __restrict__ ring_v, float* __restrict__ out,
+                        const int* __restrict__ stream_pos, int pos_base, int n_items, int ring_slots,
+                        float scale_log2e, int* status) {
+  using namespace dec;
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const uint32_t tile_bytes = static_cast<uint32_t>(ring_slots) * kRowBytes;   // one K or V slice
+  Ctl* c = reinterpret_cast<Ctl*>(smem);
+  uint8_t* stage_base = smem + ((sizeof(Ctl) + 127) & ~size_t(127));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&c->full[i], 1);
+      mbar_init(&c->empty[i], kWarps);
+    }
+    c->ctl.abort = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  CtaCtl* ctl = &c->ctl;
+
+  auto valid_slots = [&](int item) {
+    const int s = item >> 3;
+    const int pos = pos_base + (stream_pos != nullptr ? stream_pos[s] : 0);
+    return pos + 1 < ring_slots ? pos + 1 : ring_slots;   // slots 0..pos while filling, all once wrapped
+  };
+
+  if (warp == kWarps) {
+    if (lane == 0) {
+      int n = 0;
+      for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
+        const int st = n % kStages;
+        const uint32_t use = static_cast<uint32_t>(n / kStages);
+        mbar_wait(&c->empty[st], (use & 1u) ^ 1u, ctl, status, kErrWaitConsumer);
+        const uint32_t bytes = static_cast<uint32_t>(valid_slots(item)) * kRowBytes;
+        mbar_arrive_expect_tx(&c->full[st], 2 * bytes);
+        const size_t src = static_cast<size_t>(item) * ring_slots * 64;
+        bulk_load_1d(stage_base + (2 * st) * tile_bytes, ring_k + src, bytes, &c->full[st]);
+        bulk_load_1d(stage_base + (2 * st + 1) * tile_bytes, ring_v + src, bytes, &c->full[st]);
+      }
+    }
+  } else {
+    const int chunk = lane & 7;    // which 8 of the 64 head dimensions this lane owns
+    const int grp = lane >> 3;     // which of 4 consecutive slots
+    int n = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
+      const int st = n % kStages;
+      const uint32_t use = static_cast<uint32_t>(n / kStages);
+      const int nv = valid_slots(item);
+      const int s = item >> 3, h = item & 7;
+      float qf[8];
+      {
+        const uint4 raw = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(s) * 512 + h * 64 + chunk * 8);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = Pack16<__nv_bfloat16>::unpack(w[e]);
+          qf[2 * e] = f.x * scale_log2e;
+          qf[2 * e + 1] = f.y * scale_log2e;
+        }
+      }
+      mbar_wait(&c->full[st], use & 1u, ctl, status, kErrWaitTma);
+      const uint8_t* ks = stage_base + (2 * st) * tile_bytes;
+      const uint8_t* vs = stage_base + (2 * st + 1) * tile_bytes;
+
+      float sc[16];
+      float m_w = -INFINITY;
+#pragma unroll
+      for (int it = 0; it < 16; ++it) {
+        const int row = warp * 64 + it * 4 + grp;
+        float part = 0.f;
+        if (row < nv) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(ks + row * kRowBytes + chunk * 16);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = Pack16<__nv_bfloat16>::unpack(w[e]);
+            part = fmaf(qf[2 * e], f.x, part);
+            part = fmaf(qf[2 * e + 1], f.y, part);
+          }
+        }
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        sc[it] = row < nv ? part : -INFINITY;
+        m_w = fmaxf(m_w, sc[it]);
+      }
+      m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, 8));
+      m_w = fmaxf(m_w, __shfl_xor_sync(0xffffffffu, m_w, 16));
+      const float m_use = (m_w == -INFINITY) ? 0.f : m_w;
+      float l_w = 0.f;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int it = 0; it < 16; ++it) {
+        const int row = warp * 64 + it * 4 + grp;
+        if (row < nv) {
+          const float p = ex2_approx(sc[it] - m_use);
+          l_w += p;
+          const uint4 raw = *reinterpret_cast<const uint4*>(vs + row * kRowBytes + chunk * 16);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = Pack16<VT>::unpack(w[e]);
+            acc[2 * e] = fmaf(p, f.x, acc[2 * e]);
+            acc[2 * e + 1] = fmaf(p, f.y, acc[2 * e + 1]);
+          }
+        }
+      }
+      // Shared-memory reads of this stage are done: hand it back to the producer.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c->empty[st]);
+
+      l_w += __shfl_xor_sync(0xffffffffu, l_w, 8);
+      l_w += __shfl_xor_sync(0xffffffffu, l_w, 16);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
+        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+      }
+      const int mb = n & 1;
+      if (grp == 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) c->merge_o[mb][warp][chunk * 8 + e] = acc[e];
+        if (chunk == 0) {
+          c->merge_m[mb][warp] = m_w;
+          c->merge_l[mb][warp] = l_w;
+        }
+      }
+      named_bar_sync(1, kWarps * 32);
+      if (threadIdx.x < 64) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, c->merge_m[mb][w]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float f = ex2_approx(c->merge_m[mb][w] - mx);   // 0 for a warp that saw no slot
+          num = fmaf(f, c->merge_o[mb][w][threadIdx.x], num);
+          den = fmaf(f, c->merge_l[mb][w], den);
+        }
+        out[static_cast<size_t>(s) * 512 + h * 64 + threadIdx.x] = num / den;
+      }
+    }
+  }
+  __syncthreads();
+  if (ctl->abort) __nanosleep(20000);
+}
+
+int launch_ring_decode_attn(const void* q, const void* ring_k, const void* ring_v, float* out,
+                            const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
+                            int value_is_fp16, int* status, cudaStream_t st) {
+  using namespace dec;
+  if (S <= 0) return S == 0 ? 0 : -1;
+  if (ring_slots <= 0 || ring_slots > kMaxSlots || S > (1 << 27)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(ring_k) | reinterpret_cast<uintptr_t>(ring_v)) & 15u)
+    return -3;
+  const int smem_bytes = 128 + static_cast<int>((sizeof(Ctl) + 127) & ~size_t(127)) + kStages * 2 * ring_slots * kRowBytes;
+  auto kern = value_is_fp16 ? ring_decode_attn_kernel<__half> : ring_decode_attn_kernel<__nv_bfloat16>;
+  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes);
+  if (rc != 0) return rc;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int n_items = S * 8;
+  const int grid = n_items < sms ? n_items : sms;
+  kern<<<grid, kThreads, smem_bytes, st>>>(static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(ring_k),
+                                          static_cast<const uint16_t*>(ring_v), out, stream_pos, pos_base,
+                                          n_items, ring_slots, scale * 1.4426950408889634f, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fm

@@ -1,0 +1,49 @@
+// Internal launcher declarations shared by the .cu files of the library.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fm {
+
+// Where the projection epilogue puts its results.  Linear outputs are [M, 512] 16-bit tensors
+// (null = skip).  The KV ring is [clips, 8 heads, ring_slots, 64]; the frame at absolute position
+// p of a clip lands in slot p % ring_slots.
+struct QkvEpilogueArgs {
+  uint16_t* q;
+  uint16_t* k;
+  uint16_t* v;
+  uint16_t* ring_k;
+  uint16_t* ring_v;
+  const float* cos;        // [1 or clips, T, 64] FP32, as the reference's position_embeddings
+  const float* sin;
+  long long cos_bstride;   // 0 (one table for all clips) or T*64
+  const int* clip_pos;     // optional device array: absolute position of frame 0 of each clip
+  int pos_base;            // added to every position
+  int T;                   // frames per clip in this call
+  int ring_slots;
+};
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
+int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, void* base, const cuuint64_t* dims,
+                 const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* elem_strides,
+                 CUtensorMapSwizzle swizzle);
+// Opt a kernel into `bytes` of dynamic shared memory once per (kernel, device).
+int ensure_dynamic_smem(const void* kernel, int bytes);
+
+int launch_linear_fp32(const float* x, const float* w, float* y, int M, int N, int K, cudaStream_t st);
+int launch_rope_fp32(float* t, const float* cosv, const float* sinv, int B, int T, int H, int D,
+                     long long cos_bstride, cudaStream_t st);
+int launch_band_attn_fp32(const float* q, const float* k, const float* v, float* out, int B, int H, int D,
+                          int Tq, int Tk, int q_off, int k_off, int window, float scale,
+                          const long long* strides, cudaStream_t st);
+int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int value_is_fp16,
+                         int* status, cudaStream_t st);
+int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
+                             float scale, int value_is_fp16, int* status, cudaStream_t st);
+int launch_ring_decode_attn(const void* q, const void* ring_k, const void* ring_v, float* out,
+                            const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
+                            int value_is_fp16, int* status, cudaStream_t st);
+
+}  // namespace fm

@@ -1,0 +1,240 @@
+"""Tensor-level wrappers over the C ABI: validate geometry, then launch on the current stream.
+
+Validation style follows the reference's native wrappers (dtype / shape / contiguity / device checks
+raising ``RuntimeError`` before the launch: src/fast_mimi/_native_cutlass.py:126-149).  PyTorch is
+used only for device memory and streams.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+
+HIDDEN, HEADS, HEAD_DIM = 512, 8, 64
+_VALUE_CODES = {torch.bfloat16: 0, torch.float16: 1}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(f"unexpected attention geometry: {msg}")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _check_frames(t: torch.Tensor, name: str, dtype: torch.dtype, rows: int | None = None) -> None:
+    _need(t.is_cuda, f"{name} must be a CUDA tensor")
+    _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    _need(t.shape[-1] == HIDDEN, f"{name} last dimension must be {HIDDEN}")
+    if rows is not None:
+        _need(t.numel() == rows * HIDDEN, f"{name} must hold {rows} frames")
+
+
+def _check_tables(cos: torch.Tensor, sin: torch.Tensor, B: int, T: int) -> int:
+    for name, t in (("cos", cos), ("sin", sin)):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous(), f"{name} must be contiguous CUDA float32")
+        _need(t.dim() == 3 and t.shape[1] == T and t.shape[2] == HEAD_DIM and t.shape[0] in (1, B),
+              f"{name} must be [1 or {B}, {T}, {HEAD_DIM}], got {tuple(t.shape)}")
+    _need(cos.shape == sin.shape, "cos and sin must have the same shape")
+    return 0 if cos.shape[0] == 1 else T * HEAD_DIM
+
+
+_default_status: dict = {}
+
+
+def default_status(device) -> torch.Tensor:
+    """The per-device status word used when a call does not pass its own.  Once a kernel has recorded
+    a bounded-wait timeout in it, later kernels given the same word return at once; check it with
+    ``read_status(default_status(dev))`` and clear it with ``.zero_()``."""
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    st = _default_status.get(dev)
+    if st is None:
+        st = _default_status[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return st
+
+
+def _status_ptr(status, like: torch.Tensor) -> int:
+    return (default_status(like.device) if status is None else status).data_ptr()
+
+
+def new_status(device) -> torch.Tensor:
+    """A zeroed device status word for the bounded-wait error codes."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor) -> int:
+    """Synchronise the current stream and return the status word (0 = every wait completed)."""
+    return _native.load().fm_read_status(status.data_ptr(), _stream())
+
+
+def qkv_rope(x, w_qkv, cos, sin, *, value_dtype=torch.float16, out=None, status=None):
+    """``x [B,T,512] bf16`` -> rotated ``q, k`` (bf16) and ``v`` (value_dtype), each ``[B,T,512]``."""
+    lib = _native.load()
+    _need(x.dim() == 3, "x must be [B, T, 512]")
+    B, T, _ = x.shape
+    _check_frames(x, "x", torch.bfloat16)
+    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
+          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    bstride = _check_tables(cos, sin, B, T)
+    if out is None:
+        out = (torch.empty_like(x), torch.empty_like(x), torch.empty(x.shape, dtype=value_dtype, device=x.device))
+    q, k, v = out
+    _check_frames(q, "q", torch.bfloat16, B * T)
+    _check_frames(k, "k", torch.bfloat16, B * T)
+    _check_frames(v, "v", value_dtype, B * T)
+    rc = lib.fm_qkv_rope_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
+                              q.data_ptr(), k.data_ptr(), v.data_ptr(), B, T, _VALUE_CODES[value_dtype],
+                              _status_ptr(status, x), _stream())
+    _native.check(rc, "fm_qkv_rope_bf16")
+    return q, k, v
+
+
+def band_attention_prefill(q, k, v, *, window=250, scale=0.125, out=None, status=None):
+    """Banded causal attention over rotated ``q, k [B,T,512] bf16`` and ``v [B,T,512]`` (fp16 or bf16)."""
+    lib = _native.load()
+    _need(q.dim() == 3, "q must be [B, T, 512]")
+    B, T, _ = q.shape
+    _check_frames(q, "q", torch.bfloat16)
+    _check_frames(k, "k", torch.bfloat16, B * T)
+    _need(v.dtype in _VALUE_CODES, "v must be float16 or bfloat16")
+    _check_frames(v, "v", v.dtype, B * T)
+    if out is None:
+        out = torch.empty_like(v)
+    _check_frames(out, "out", v.dtype, B * T)
+    rc = lib.fm_band_attn_prefill_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, T, window,
+                                       scale, _VALUE_CODES[v.dtype], _status_ptr(status, q), _stream())
+    _native.check(rc, "fm_band_attn_prefill_bf16")
+    return out
+
+
+def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtype=torch.float16,
+                      workspace=None, out=None, status=None):
+    """Projection + RoPE + banded attention for a call without cache; returns ``[B,T,512]`` value_dtype."""
+    lib = _native.load()
+    _need(x.dim() == 3, "x must be [B, T, 512]")
+    B, T, _ = x.shape
+    _check_frames(x, "x", torch.bfloat16)
+    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
+          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    bstride = _check_tables(cos, sin, B, T)
+    if workspace is None:
+        workspace = (torch.empty_like(x), torch.empty_like(x),
+                     torch.empty(x.shape, dtype=value_dtype, device=x.device))
+    q, k, v = workspace
+    _check_frames(q, "q workspace", torch.bfloat16, B * T)
+    _check_frames(k, "k workspace", torch.bfloat16, B * T)
+    _check_frames(v, "v workspace", value_dtype, B * T)
+    if out is None:
+        out = torch.empty(x.shape, dtype=value_dtype, device=x.device)
+    _check_frames(out, "out", value_dtype, B * T)
+    rc = lib.fm_attention_prefill_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
+                                       q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, T, window,
+                                       scale, _VALUE_CODES[value_dtype], _status_ptr(status, x), _stream())
+    _native.check(rc, "fm_attention_prefill_bf16")
+    return out
+
+
+def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_workspace=None, out=None,
+                stream_pos=None, status=None):
+    """One streaming step.  ``x [S,512] bf16``; ``ring_k/ring_v [S,8,slots,64]``; the new frame of
+    stream s has absolute position ``position + stream_pos[s]``.  Returns ``[S,512] float32``."""
+    lib = _native.load()
+    _need(x.dim() == 2, "x must be [S, 512]")
+    S = x.shape[0]
+    _check_frames(x, "x", torch.bfloat16)
+    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
+          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    bstride = 0 if cos.shape[0] == 1 else HEAD_DIM
+    _check_tables(cos, sin, S, 1)
+    _need(ring_k.dim() == 4 and ring_k.shape[0] == S and ring_k.shape[1] == HEADS and ring_k.shape[3] == HEAD_DIM,
+          "ring_k must be [S, 8, slots, 64]")
+    slots = ring_k.shape[2]
+    _need(ring_k.is_cuda and ring_k.dtype == torch.bfloat16 and ring_k.is_contiguous(), "ring_k must be contiguous bf16")
+    _need(ring_v.is_cuda and ring_v.dtype in _VALUE_CODES and ring_v.is_contiguous()
+          and ring_v.shape == ring_k.shape, "ring_v must match ring_k (float16 or bfloat16)")
+    if stream_pos is not None:
+        _need(stream_pos.is_cuda and stream_pos.dtype == torch.int32 and stream_pos.numel() == S
+              and stream_pos.is_contiguous(), "stream_pos must be a contiguous CUDA int32 [S]")
+    if q_workspace is None:
+        q_workspace = torch.empty_like(x)
+    _check_frames(q_workspace, "q workspace", torch.bfloat16, S)
+    if out is None:
+        out = torch.empty((S, HIDDEN), dtype=torch.float32, device=x.device)
+    _need(out.is_cuda and out.dtype == torch.float32 and out.is_contiguous() and out.numel() == S * HIDDEN,
+          "out must be contiguous float32 [S, 512]")
+    rc = lib.fm_decode_step_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
+                                 _ptr(stream_pos), int(position), q_workspace.data_ptr(), ring_k.data_ptr(),
+                                 ring_v.data_ptr(), out.data_ptr(), S, slots, scale, _VALUE_CODES[ring_v.dtype],
+                                 _status_ptr(status, x), _stream())
+    _native.check(rc, "fm_decode_step_bf16")
+    return out
+
+
+def _strides3(t: torch.Tensor, frame_major: bool) -> list[int]:
+    # (batch, head, time) strides in elements for a 4-D tensor whose last dim is contiguous.
+    if frame_major:     # [B, T, H, D]
+        return [t.stride(0), t.stride(2), t.stride(1)]
+    return [t.stride(0), t.stride(1), t.stride(2)]   # [B, H, T, D]
+
+
+def band_attention_fp32(q, k, v, *, window, scale, q_offset=0, k_offset=0, frame_major=False, out=None):
+    """FP32 verification attention.  ``q [B,H,Tq,D]``, ``k, v [B,H,Tk,D]`` (or ``[B,T,H,D]`` with
+    ``frame_major=True``); any strides with a contiguous last dimension.  Returns a tensor shaped like q."""
+    lib = _native.load()
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.dim() == 4 and t.stride(-1) == 1,
+              f"{name} must be a 4-D CUDA float32 tensor with a contiguous last dimension")
+    if frame_major:
+        B, Tq, H, D = q.shape
+        Tk = k.shape[1]
+    else:
+        B, H, Tq, D = q.shape
+        Tk = k.shape[2]
+    _need(k.shape == v.shape and k.shape[0] == B and k.shape[-1] == D, "k and v must match q in batch/heads/head_dim")
+    _need(D <= 256, "head_dim must be at most 256")
+    if out is None:
+        out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    _need(out.shape == q.shape and out.dtype == torch.float32 and out.stride(-1) == 1, "out must be shaped like q")
+    strides = _strides3(q, frame_major) + _strides3(k, frame_major) + _strides3(v, frame_major) + _strides3(out, frame_major)
+    import ctypes
+    arr = (ctypes.c_longlong * 12)(*strides)
+    rc = lib.fm_band_attn_fp32_verify(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, D, Tq, Tk,
+                                      int(q_offset), int(k_offset), int(window), float(scale),
+                                      ctypes.cast(arr, ctypes.c_void_p), _stream())
+    _native.check(rc, "fm_band_attn_fp32_verify")
+    return out
+
+
+def linear_fp32(x, w):
+    """``x [..., K] @ w[N, K]^T`` in FP32 on CUDA cores (verification path)."""
+    lib = _native.load()
+    _need(x.is_cuda and w.is_cuda and x.dtype == torch.float32 and w.dtype == torch.float32, "float32 CUDA tensors")
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    w = w.contiguous()
+    _need(x2.shape[1] == w.shape[1], "inner dimensions differ")
+    y = torch.empty((x2.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+    rc = lib.fm_linear_fp32_verify(x2.data_ptr(), w.data_ptr(), y.data_ptr(), x2.shape[0], w.shape[0], x2.shape[1],
+                                   _stream())
+    _native.check(rc, "fm_linear_fp32_verify")
+    return y.view(*x.shape[:-1], w.shape[0])
+
+
+def rope_fp32_(t, cos, sin):
+    """In-place RoPE on ``t [B,T,H,D]`` FP32 with ``cos, sin [1 or B, T, D]``."""
+    lib = _native.load()
+    _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.dim() == 4, "t must be contiguous [B,T,H,D]")
+    B, T, H, D = t.shape
+    cos, sin = cos.contiguous().float(), sin.contiguous().float()
+    _need(cos.dim() == 3 and cos.shape[1] == T and cos.shape[2] == D and cos.shape[0] in (1, B), "bad cos shape")
+    bstride = 0 if cos.shape[0] == 1 else T * D
+    rc = lib.fm_rope_fp32_verify(t.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, T, H, D, bstride, _stream())
+    _native.check(rc, "fm_rope_fp32_verify")
+    return t

@@ -1,0 +1,93 @@
+/* fast_mimi_b200 — C ABI of the B200 (sm_100a) kernels for Mimi's transformer self-attention.
+ *
+ * Conventions (the reference's own native-launcher convention: `extern "C" int fn(void* ptrs...,
+ * int dims..., void* stream)`, e.g. src/fast_mimi/_native_cutlass.py:110-116 binding
+ * src/fast_mimi/cutlass_bias_dgrad.cu:147-157):
+ *   - every pointer is a raw DEVICE pointer owned by the caller; nothing is allocated or freed here;
+ *   - `stream` is a cudaStream_t (0 = legacy default stream); launches are asynchronous on it;
+ *   - the return value is 0 on success, a positive cudaError_t / CUresult, or a negative code for a
+ *     rejected geometry (-1 bad size, -3 misaligned pointer, -4 driver entry point unavailable);
+ *   - `status` (optional, may be NULL) is a caller-zeroed device int; a kernel whose bounded wait on
+ *     a TMA / tensor-core completion barrier runs out writes a code >= 101 there and finishes early.
+ *     Read it back with fm_read_status().
+ *   - geometry of the tensor-core entry points is Mimi's: hidden 512, 8 heads of 64.
+ *   - value_dtype: 0 = BF16, 1 = FP16: storage type of V, of the softmax probabilities fed to the
+ *     tensor core, and of the prefill output.  Q and K are always BF16.
+ *
+ * Tensors named "frames" are [B, T, 512] row-major (heads are 64-column slices), which is the
+ * memory layout behind the reference's [B, 8, T, 64] strided views (src/fast_mimi/model.py:1897-1911).
+ */
+#ifndef FAST_MIMI_B200_H_
+#define FAST_MIMI_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int fm_abi_version(void);
+
+/* q|k|v = x W_qkv^T with rotate-half RoPE applied to q and k in the FP32 epilogue.
+ * Replaces q_proj/k_proj/v_proj + _apply_rope (src/fast_mimi/model.py:1897-1912; packed-weight form
+ * src/fast_mimi/_packed_qkv.py:139-171).
+ *   x      [B*T, 512] BF16          w_qkv [1536, 512] BF16 = cat(Wq, Wk, Wv) rows
+ *   cos,sin [1 or B, T, 64] FP32 (the reference's position_embeddings); cos_bstride = 0 or T*64
+ *   q,k    [B*T, 512] BF16 out      v [B*T, 512] value_dtype out */
+int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
+                     long long cos_bstride, void* q, void* k, void* v, int B, int T, int value_dtype,
+                     int* status, void* stream);
+
+/* Banded causal attention over already-rotated q, k: key j visible to query i iff i-window < j <= i.
+ * Replaces _sdpa_fallback's masked SDPA (src/fast_mimi/model.py:1823-1868, mask :1672-1676) and
+ * _native_window_attention (src/fast_mimi/model.py:1589-1624).
+ *   q,k [B, T, 512] BF16; v, out [B, T, 512] value_dtype.  scale is applied to q.k (0.125 for Mimi). */
+int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int B, int T,
+                              int window, float scale, int value_dtype, int* status, void* stream);
+
+/* fm_qkv_rope_bf16 followed by fm_band_attn_prefill_bf16 on the same stream: the part of
+ * MimiAttention.forward between the input and o_proj (src/fast_mimi/model.py:1896-1951) for a call
+ * without cache.  q_ws/k_ws/v_ws are caller-provided workspaces of B*T*512 16-bit elements each. */
+int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
+                              long long cos_bstride, void* q_ws, void* k_ws, void* v_ws, void* out, int B,
+                              int T, int window, float scale, int value_dtype, int* status, void* stream);
+
+/* One streaming step for S streams: project the new frame, rotate q/k at the stream's position,
+ * write k/v into slot (position % ring_slots) of the stream's ring, attend over the valid slots.
+ * Replaces MimiKVCache.update + one-query SDPA (src/fast_mimi/model.py:1912-1914, 435-471, 1860-1868).
+ *   x [S, 512] BF16; cos,sin [1 or S, 1, 64] FP32 at each stream's position (cos_bstride 0 or 64)
+ *   stream_pos: optional device int[S]; position of the new frame = pos_base + stream_pos[s]
+ *   q_ws [S, 512] BF16 workspace; ring_k BF16 / ring_v value_dtype: [S, 8, ring_slots, 64]
+ *   out [S, 512] FP32.  ring_slots = sliding window (250 for Mimi), at most 256. */
+int fm_decode_step_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
+                        long long cos_bstride, const int* stream_pos, int pos_base, void* q_ws, void* ring_k,
+                        void* ring_v, float* out, int S, int ring_slots, float scale, int value_dtype,
+                        int* status, void* stream);
+
+/* The attention half of the step alone (q and the ring already hold the new frame). */
+int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring_v, float* out,
+                             const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
+                             int value_dtype, int* status, void* stream);
+
+/* FP32 verification path on CUDA cores, generic in heads / head_dim (<= 256) / window / offsets.
+ * Same semantics as the eager branch of the reference (src/fast_mimi/model.py:1953-1958) with the
+ * mask of _attention_mask at absolute positions (src/fast_mimi/model.py:1672-1676):
+ * query i has position i+q_off, key j has position j+k_off.
+ * strides[12] = {q_b,q_h,q_t, k_b,k_h,k_t, v_b,v_h,v_t, out_b,out_h,out_t} in elements; head_dim is
+ * contiguous.  q, k already rotated. */
+int fm_band_attn_fp32_verify(const float* q, const float* k, const float* v, float* out, int B, int H, int D,
+                             int Tq, int Tk, int q_off, int k_off, int window, float scale,
+                             const long long* strides, void* stream);
+
+/* y[M,N] = x[M,K] w[N,K]^T in FP32 (F.linear without bias, src/fast_mimi/_functional_runtime.py:138-141). */
+int fm_linear_fp32_verify(const float* x, const float* w, float* y, int M, int N, int K, void* stream);
+
+/* In-place rotate-half RoPE on t [B, T, H, D] FP32 (src/fast_mimi/model.py:1538-1569). */
+int fm_rope_fp32_verify(float* t, const float* cos, const float* sin, int B, int T, int H, int D,
+                        long long cos_bstride, void* stream);
+
+/* Synchronise `stream` and return the device status word (0 = all bounded waits completed). */
+int fm_read_status(const int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FAST_MIMI_B200_H_ */

@@ -1,0 +1,178 @@
+"""Tensor-core path (tcgen05 projection + banded attention + ring decode) vs golden fixtures and the
+CPU oracle.  Parity metric: relative L2 of the attention output <= 2e-3 (north-star tolerance)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import load_golden, regen_attention_layer
+from oracle import mimi_attention_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3           # attention output, relative L2
+TOL_BF16_STORE = 4e-3  # q/k intermediates: one BF16 rounding of an FP32 result (not the parity metric)
+
+
+def _frames(t):    # [B,H,T,D] -> [B,T,H*D]
+    b, h, n, d = t.shape
+    return t.transpose(1, 2).contiguous().view(b, n, h * d)
+
+
+def _status_ok(st):
+    import fast_mimi_b200 as fm
+    assert fm.ops.read_status(st) == 0
+
+
+def test_qkv_projection_rope_matches_oracle():
+    import fast_mimi_b200 as fm
+    torch.manual_seed(3)
+    B, T = 3, 250
+    x = torch.randn(B, T, 512).bfloat16()
+    w = (torch.randn(1536, 512) * 0.02).bfloat16()
+    cos, sin = O.rope_tables(torch.arange(T))
+    q, k, v = O.qkv_project(x.float(), *w.float().chunk(3, 0))
+    q, k = O.apply_rope(q, k, cos, sin)
+    st = fm.ops.new_status("cuda")
+    gq, gk, gv = fm.ops.qkv_rope(x.cuda(), w.cuda(), cos.cuda()[None], sin.cuda()[None], status=st)
+    _status_ok(st)
+    assert gv.dtype == torch.float16
+    assert O.rel_l2(gq.float().cpu(), _frames(q)) < TOL_BF16_STORE
+    assert O.rel_l2(gk.float().cpu(), _frames(k)) < TOL_BF16_STORE
+    assert O.rel_l2(gv.float().cpu(), _frames(v)) < 5e-4
+
+
+def test_qkv_projection_ragged_rows_and_per_clip_tables():
+    """M = B*T not a multiple of the 128-row tile; cos/sin given per clip."""
+    import fast_mimi_b200 as fm
+    torch.manual_seed(4)
+    B, T = 5, 37
+    x = torch.randn(B, T, 512).bfloat16()
+    w = (torch.randn(1536, 512) * 0.02).bfloat16()
+    tabs = [O.rope_tables(torch.arange(10 * b, 10 * b + T)) for b in range(B)]
+    cos = torch.stack([t[0] for t in tabs]); sin = torch.stack([t[1] for t in tabs])
+    q, k, v = O.qkv_project(x.float(), *w.float().chunk(3, 0))
+    q, k = O.apply_rope(q, k, cos, sin)
+    gq, gk, gv = fm.ops.qkv_rope(x.cuda(), w.cuda(), cos.cuda(), sin.cuda(), value_dtype=torch.bfloat16)
+    assert O.rel_l2(gq.float().cpu(), _frames(q)) < TOL_BF16_STORE
+    assert O.rel_l2(gk.float().cpu(), _frames(k)) < TOL_BF16_STORE
+    assert O.rel_l2(gv.float().cpu(), _frames(v)) < TOL_BF16_STORE
+
+
+def test_isolated_op_config2_matches_golden():
+    import fast_mimi_b200 as fm
+    g = load_golden("isolated_T250.npz")
+    gen = torch.Generator().manual_seed(int(g["seed"]))
+    q, k, v = (torch.randn(1, 8, 250, 64, generator=gen) / 8 for _ in range(3))
+    cos, sin = O.rope_tables(torch.arange(250))
+    qr, kr = O.apply_rope(q, k, cos, sin)
+    out = fm.native_window_attention(qr.cuda(), kr.cuda(), v.cuda(), scale=0.125, window=250)
+    assert out.shape == (1, 8, 250, 64) and out.dtype == torch.float32
+    assert O.rel_l2(out[0][:, g["rows"]].cpu(), g["out"]) < TOL
+
+
+def test_long_band_T700_matches_golden():
+    import fast_mimi_b200 as fm
+    g = load_golden("band_T700.npz")
+    gen = torch.Generator().manual_seed(int(g["seed"]))
+    q, k, v = (torch.randn(1, 8, 700, 64, generator=gen) / 8 for _ in range(3))
+    cos, sin = O.rope_tables(torch.arange(700))
+    qr, kr = O.apply_rope(q, k, cos, sin)
+    out = fm.native_window_attention(qr.cuda(), kr.cuda(), v.cuda(), scale=0.125, window=250)
+    assert O.rel_l2(out[0][:, g["rows"]].cpu(), g["out"]) < TOL
+
+
+@pytest.mark.parametrize("T", [1, 2, 63, 64, 65, 125, 127, 128, 129, 249, 250, 251, 313, 513])
+@pytest.mark.parametrize("window", [250])
+def test_odd_lengths_match_oracle(T, window):
+    import fast_mimi_b200 as fm
+    gen = torch.Generator().manual_seed(T)
+    q, k, v = (torch.randn(2, 8, T, 64, generator=gen) / 2 for _ in range(3))
+    ref = O.band_attention(q, k, v, window=window, scale=0.125)
+    out = fm.native_window_attention(q.cuda(), k.cuda(), v.cuda(), scale=0.125, window=window)
+    assert O.rel_l2(out.cpu(), ref) < TOL
+    assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("window", [1, 8, 100, 128, 129, 300])
+def test_other_windows_match_oracle(window):
+    import fast_mimi_b200 as fm
+    gen = torch.Generator().manual_seed(window)
+    q, k, v = (torch.randn(1, 8, 400, 64, generator=gen) / 2 for _ in range(3))
+    ref = O.band_attention(q, k, v, window=window, scale=0.125)
+    out = fm.native_window_attention(q.cuda(), k.cuda(), v.cuda(), scale=0.125, window=window)
+    assert O.rel_l2(out.cpu(), ref) < TOL
+
+
+def test_bf16_value_path_is_available_and_close():
+    """value_dtype=bfloat16 (the literal BF16 cache) is supported; its rounding alone costs ~2e-3."""
+    import fast_mimi_b200 as fm
+    gen = torch.Generator().manual_seed(21)
+    q, k, v = (torch.randn(1, 8, 250, 64, generator=gen) / 2 for _ in range(3))
+    ref = O.band_attention(q, k, v, scale=0.125)
+    out = fm.native_window_attention(q.cuda(), k.cuda(), v.cuda(), scale=0.125, window=250,
+                                     value_dtype=torch.bfloat16)
+    assert O.rel_l2(out.cpu(), ref) < 6e-3
+
+
+@pytest.mark.parametrize("name", ["attention_layer_T250.npz", "attention_layer_T313.npz"])
+def test_attention_module_matches_reference_layer(name):
+    """MimiAttentionB200 (tensor-core path, o_proj included) vs the reference MimiAttention output."""
+    import fast_mimi_b200 as fm
+    g = load_golden(name)
+    x, wq, wk, wv, wo = regen_attention_layer(int(g["seed"]), int(g["b"]), int(g["t"]))
+    assert torch.equal(x[0, :2, :8], g["x_probe"])
+    m = fm.MimiAttentionB200().cuda()
+    with torch.no_grad():
+        for lin, w in zip((m.q_proj, m.k_proj, m.v_proj, m.o_proj), (wq, wk, wv, wo)):
+            lin.weight.copy_(w)
+    cos, sin = O.rope_tables(torch.arange(x.shape[1]))
+    out, weights = m(x.cuda(), None, None, (cos.cuda()[None], sin.cuda()[None]))
+    assert weights is None and out.dtype == torch.float32
+    assert O.rel_l2(out[:, g["rows"]].cpu(), g["out"]) < TOL
+
+
+def test_streaming_decode_260_steps_matches_reference():
+    """260 one-frame steps through the KV ring (fills, then wraps at step 250) vs the reference's
+    MimiKVCache + SDPA outputs; the ring must hold the same rows as the reference cache."""
+    import fast_mimi_b200 as fm
+    g = load_golden("ring_decode_260.npz")
+    torch.manual_seed(int(g["seed"]))
+    lins = [torch.nn.Linear(512, 512, bias=False) for _ in range(4)]
+    for lin in lins:
+        torch.nn.init.normal_(lin.weight, std=0.02)
+    m = fm.MimiAttentionB200().cuda()
+    with torch.no_grad():
+        for dst, src in zip((m.q_proj, m.k_proj, m.v_proj, m.o_proj), lins):
+            dst.weight.copy_(src.weight)
+    cache = m.new_cache(1, 2, "cuda")
+    keep = g["keep_steps"].tolist()
+    got = []
+    for step in range(260):
+        x = torch.randn(2, 1, 512)
+        cos, sin = O.rope_tables(torch.arange(step, step + 1))
+        out, _ = m(x.cuda(), None, cache, (cos.cuda()[None], sin.cuda()[None]))
+        if step in keep:
+            got.append(out.cpu())
+    assert cache.get_seq_length() == 260
+    got = torch.stack(got)
+    for i, step in enumerate(keep):
+        assert O.rel_l2(got[i], g["outs"][i]) < TOL, step
+    k_ord, v_ord = cache.ordered(0)
+    assert k_ord.shape[2] == 250
+    assert O.rel_l2(k_ord[:, :, -3:].float().cpu(), g["final_key_cache"]) < TOL_BF16_STORE
+    assert O.rel_l2(v_ord[:, :, -3:].float().cpu(), g["final_value_cache"]) < 5e-4
+
+
+def test_module_rejects_what_it_does_not_implement():
+    import fast_mimi_b200 as fm
+    m = fm.MimiAttentionB200().cuda()
+    x = torch.zeros(1, 4, 512, device="cuda")
+    cs = tuple(t.cuda()[None] for t in O.rope_tables(torch.arange(4)))
+    with pytest.raises(RuntimeError):
+        m(x, None, None, cs, output_attentions=True)
+    with pytest.raises(RuntimeError):
+        m(x, torch.ones(1, 4, device="cuda"), None, cs)            # key-padding mask
+    with pytest.raises(RuntimeError):
+        m(x.cpu(), None, None, cs)                                   # no CPU path
+    with pytest.raises(RuntimeError):
+        fm.ops.band_attention_prefill(x, x, x)                       # wrong dtype
