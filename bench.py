@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the Mimi attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 3, "batched prefill"): per GPU 512 clips of 250 frames (10 s at 25 Hz)
+through the attention path of 16 transformer layers (8 encoder + 8 decoder): QKV projection + RoPE +
+banded causal attention (window 250), BF16 inputs, FP32 accumulate.  One step = one pass of the 16
+layers over the batch.  Metric: attention frames/s = clips * frames * layers / time, summed over GPUs.
+Clips are independent, so ranks share nothing on the data path (weak scaling: 512 clips per GPU).
+
+One JSON line is printed by rank 0.  `value` is device-resident throughput; `e2e` includes the
+host->device copy of the batch from pinned memory and the device->host copy of the last layer's output
+every step.  `roofline` describes the kernel with the largest share of the step, timed with CUDA events
+on the launching stream inside the timed region.  `cpu_baseline` is the CPU oracle (a PyTorch FP32
+restatement of the reference's attention, all host threads) on a bounded sample of the same workload.
+`decode` adds the streaming single-frame step (BASELINE config 5) on a full 250-slot ring.
+
+`--impl reference` times that CPU restatement instead (the reference is PyTorch code whose CPU path is
+exactly these library calls; the reference checkout itself does not travel to the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CLIPS, FRAMES, LAYERS, HIDDEN, WINDOW = 512, 250, 16, 512, 250
+QKV_FLOP_PER_FRAME = 2 * 512 * 1536
+
+
+def pairs(t: int, window: int = WINDOW) -> int:
+    return sum(min(i + 1, window) for i in range(t))
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.samples.append([c.strip() for c in out.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self.samples[0][1]),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- CPU oracle timing
+def cpu_oracle_step(sample_clips: int, layers: int, seed: int = 1):
+    """One pass of the oracle's attention path over `sample_clips` clips x `layers` layers."""
+    from oracle import mimi_attention_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(sample_clips, FRAMES, HIDDEN, generator=g)
+    ws = [(torch.randn(1536, HIDDEN, generator=g) * 0.02) for _ in range(layers)]
+    cos, sin = O.rope_tables(torch.arange(FRAMES))
+
+    def run():
+        out = None
+        for w in ws:
+            q, k, v = O.qkv_project(x, *w.chunk(3, 0))
+            q, k = O.apply_rope(q, k, cos, sin)
+            out = O.band_attention_sdpa(q, k, v)
+        return out
+
+    return run
+
+
+def time_cpu_oracle(budget_s: float = 12.0) -> dict:
+    torch.set_num_threads(os.cpu_count() or 1)
+    probe = cpu_oracle_step(4, 1)
+    probe()
+    t0 = time.perf_counter(); probe(); dt = time.perf_counter() - t0
+    per_clip_layer = dt / 4
+    clips = int(max(4, min(CLIPS, budget_s / (per_clip_layer * LAYERS))))
+    run = cpu_oracle_step(clips, LAYERS)
+    run()
+    t0 = time.perf_counter(); run(); dt = time.perf_counter() - t0
+    return {"value": clips * FRAMES * LAYERS / dt, "unit": "frames/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": f"{clips} of {CLIPS} clips x {FRAMES} frames x {LAYERS} layers, FP32, "
+                                      f"{dt:.2f} s, one repetition after warm-up"}
+
+
+def run_reference(args) -> None:
+    """The reference's CPU path (restated in oracle/) on host cores, same metric and config."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    probe = cpu_oracle_step(4, 1)
+    probe()
+    t0 = time.perf_counter(); probe(); dt = time.perf_counter() - t0
+    total_steps = args.steps + args.warmup
+    clips = int(max(2, min(CLIPS, 120.0 / total_steps / (dt / 4 * LAYERS))))
+    run = cpu_oracle_step(clips, LAYERS)
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    elapsed = time.perf_counter() - t0
+    ms = elapsed / args.steps * 1e3
+    value = clips * FRAMES * LAYERS / (ms / 1e3)
+    cpu = {"value": value, "unit": "frames/s", "cores": torch.get_num_threads(), "kind": "port",
+           "sample": f"each step = {clips} of {CLIPS} clips x {FRAMES} frames x {LAYERS} layers, FP32"}
+    print(json.dumps({
+        "impl": "reference", "metric": "attention frames/s", "value": value, "unit": "frames/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(), "cpu_baseline": cpu,
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def config_dict() -> dict:
+    return {"workload": "batched prefill (BASELINE config 3): QKV projection + RoPE + banded causal attention, "
+                        "16 layers", "clips_per_gpu": CLIPS, "frames": FRAMES, "layers": LAYERS, "window": WINDOW,
+            "heads": 8, "head_dim": 64, "l2": "inputs larger than L2: each layer streams 655 MB (x, q, k, v, out)"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args) -> None:
+    import torch.distributed as dist
+    import fast_mimi_b200 as fm
+    from fast_mimi_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    x = torch.randn(CLIPS, FRAMES, HIDDEN, device=dev, generator=g).bfloat16()
+    ws = [(torch.randn(1536, HIDDEN, device=dev, generator=g) * 0.02).bfloat16() for _ in range(LAYERS)]
+    pos = torch.arange(FRAMES, device=dev, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, 2, device=dev, dtype=torch.int64).float() / 64))
+    freqs = torch.outer(pos, inv)
+    emb = torch.cat((freqs, freqs), -1)
+    cos, sin = emb.cos()[None].contiguous(), emb.sin()[None].contiguous()
+    q = torch.empty_like(x); k = torch.empty_like(x)
+    v = torch.empty(x.shape, dtype=torch.float16, device=dev)
+    out = torch.empty(x.shape, dtype=torch.float16, device=dev)
+    status = ops.new_status(dev)
+    stream = torch.cuda.current_stream()
+
+    def step(events=None):
+        for l in range(LAYERS):
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record(stream)
+            ops.qkv_rope(x, ws[l], cos, sin, out=(q, k, v), status=status)
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True); e1.record(stream)
+            ops.band_attention_prefill(q, k, v, window=WINDOW, scale=0.125, out=out, status=status)
+            if events is not None:
+                e2 = torch.cuda.Event(enable_timing=True); e2.record(stream)
+                events.append((e0, e1, e2))
+
+    # ---- device-resident throughput ---------------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    events: list = []
+    start = torch.cuda.Event(enable_timing=True); stop = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        start.record(stream)
+        for _ in range(args.steps):
+            step(events)
+        stop.record(stream)
+        barrier()
+    ms_total = start.elapsed_time(stop)
+    if ops.read_status(status) != 0:
+        raise SystemExit(f"a bounded device wait timed out (status {ops.read_status(status)})")
+    gemm_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in events)
+    attn_ms = statistics.mean(b.elapsed_time(c) for _, b, c in events)
+
+    # ---- end to end: pinned host input -> device -> 16 layers -> host --------------------------
+    x_host = torch.empty(x.shape, dtype=x.dtype, pin_memory=True); x_host.copy_(x)
+    out_host = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        out_host.copy_(out, non_blocking=True)
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    s2 = torch.cuda.Event(enable_timing=True); t2 = torch.cuda.Event(enable_timing=True)
+    s2.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    t2.record(stream)
+    barrier()
+    ms_e2e = s2.elapsed_time(t2)
+
+    # ---- streaming decode (BASELINE config 5) on a full ring ----------------------------------
+    decode = None
+    if not args.no_decode:
+        decode = bench_decode(dev, stream, peaks, world, rank)
+
+    times = torch.tensor([ms_total, ms_e2e, gemm_ms, attn_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e, gemm_ms, attn_ms = times.tolist()
+    frames_per_step = CLIPS * FRAMES * LAYERS * world
+    ms_per_step = ms_total / args.steps
+    value = frames_per_step / (ms_per_step / 1e3)
+    e2e_value = frames_per_step / (ms_e2e / args.steps / 1e3)
+
+    rows = CLIPS * FRAMES
+    gemm_flop = rows * QKV_FLOP_PER_FRAME
+    attn_flop = CLIPS * 2048 * pairs(FRAMES)
+    attn_bytes = 4 * rows * HIDDEN * 2
+    gemm_tf = gemm_flop / (gemm_ms / 1e3) / 1e12
+    attn_gbs = attn_bytes / (attn_ms / 1e3) / 1e9
+    kernels = [
+        {"kernel": "qkv_rope_gemm_kernel", "ms": gemm_ms, "share": gemm_ms / (gemm_ms + attn_ms), "bound": "tensor",
+         "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": gemm_tf / peaks["bf16_tflops"]},
+        {"kernel": "band_attn_prefill_kernel", "ms": attn_ms, "share": attn_ms / (gemm_ms + attn_ms), "bound": "hbm",
+         "achieved": attn_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn_gbs / peaks["hbm_gbs"],
+         "tensor_tflops": attn_flop / (attn_ms / 1e3) / 1e12},
+    ]
+    top = max(kernels, key=lambda d: d["ms"])
+    roofline = {"bound": top["bound"], "achieved": top["achieved"], "peak": top["peak"], "unit": top["unit"],
+                "frac": top["frac"], "traffic": None, "kernel": top["kernel"],
+                "peak_source": f"{peaks['source']} (burst figure)", "avg_launch_ms": top["ms"]}
+
+    if rank == 0:
+        cpu = time_cpu_oracle() if world == 1 and not args.no_cpu else None
+        line = {
+            "metric": "attention frames/s", "value": value, "unit": "frames/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(),
+            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": x.numel() * 2,
+                    "d2h_bytes_per_step": out.numel() * 2, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": args.steps * LAYERS * 2, "roofline": roofline, "kernels": kernels,
+            "clocks": clocks.summary(), "cpu_baseline": cpu, "decode": decode,
+            "step_tflops": (gemm_flop + attn_flop) * LAYERS / (ms_per_step / 1e3) / 1e12,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def bench_decode(dev, stream, peaks, world, rank, streams: int = 4096, layers: int = 8, steps: int = 20) -> dict:
+    """Full-ring streaming steps: 4096 streams x 8 layers, ring position >= 250 (every slot valid)."""
+    import torch.distributed as dist
+    import fast_mimi_b200 as fm
+    from fast_mimi_b200 import ops
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    ring = fm.MimiKVRing(layers, streams, WINDOW, device=dev)
+    ring.ring_k.copy_((torch.randn(ring.ring_k.shape[1:], device=dev, generator=g) / 2).bfloat16().expand_as(ring.ring_k))
+    ring.ring_v.copy_((torch.randn(ring.ring_v.shape[1:], device=dev, generator=g) / 2).half().expand_as(ring.ring_v))
+    ws = [(torch.randn(1536, HIDDEN, device=dev, generator=g) * 0.02).bfloat16() for _ in range(layers)]
+    xs = torch.randn(streams, HIDDEN, device=dev, generator=g).bfloat16()
+    cos = torch.ones(1, 1, 64, device=dev); sin = torch.zeros(1, 1, 64, device=dev)
+    qws = torch.empty_like(xs)
+    out = torch.empty(streams, HIDDEN, device=dev, dtype=torch.float32)
+    status = ops.new_status(dev)
+
+    def one_step(pos, events=None):
+        for l in range(layers):
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record(stream)
+            ops.decode_step(xs, ws[l], cos, sin, ring.ring_k[l], ring.ring_v[l], pos, q_workspace=qws, out=out,
+                            status=status)
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True); e1.record(stream)
+                events.append((e0, e1))
+
+    for i in range(3):
+        one_step(250 + i)
+    torch.cuda.synchronize()
+    events: list = []
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for i in range(steps):
+        one_step(253 + i, events)
+    b.record(stream)
+    torch.cuda.synchronize()
+    if ops.read_status(status) != 0:
+        raise SystemExit("decode: a bounded device wait timed out")
+    ms = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms)
+    layer_ms = statistics.mean(x.elapsed_time(y) for x, y in events)
+    # algorithmic bytes per (stream, layer, step): ring read 2*250*512*2, ring write 2048, x 1024 (bf16), out 2048
+    per_stream = 2 * WINDOW * 512 * 2 + 2048 + 1024 + 2048
+    bytes_layer = streams * per_stream + 1536 * 512 * 2
+    gbs = bytes_layer / (layer_ms / 1e3) / 1e9
+    del ring
+    torch.cuda.empty_cache()
+    return {"workload": "streaming decode (BASELINE config 5), full 250-slot ring", "streams_per_gpu": streams,
+            "layers": layers, "steps": steps, "ms_per_step": ms_step,
+            "value": streams * layers * world / (ms_step / 1e3), "unit": "frames/s",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "kernel": "qkv_rope_gemm_kernel + ring_decode_attn_kernel",
+                         "avg_layer_ms": layer_ms, "bytes_per_layer_step": bytes_layer}}
+
+
+def profile_case(which: str) -> None:
+    """Small cases for `ncu --set full` captures (inputs above the 126 MB L2, well under a few GB,
+    a handful of launches): prefill = 256 clips x 250 frames, one layer; decode = 512 streams on a
+    full ring, one layer.  Prints nothing that is a benchmark value."""
+    import fast_mimi_b200 as fm
+    from fast_mimi_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    w = (torch.randn(1536, HIDDEN, device=dev, generator=g) * 0.02).bfloat16()
+    if which == "prefill":
+        x = torch.randn(256, FRAMES, HIDDEN, device=dev, generator=g).bfloat16()
+        cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)
+        for _ in range(4):
+            ops.attention_prefill(x, w, cos, sin)
+    else:
+        ring = fm.MimiKVRing(1, 512, WINDOW, device=dev)
+        ring.ring_k.copy_((torch.randn(ring.ring_k.shape, device=dev, generator=g) / 2).bfloat16())
+        ring.ring_v.copy_((torch.randn(ring.ring_v.shape, device=dev, generator=g) / 2).half())
+        xs = torch.randn(512, HIDDEN, device=dev, generator=g).bfloat16()
+        cos = torch.ones(1, 1, 64, device=dev); sin = torch.zeros(1, 1, 64, device=dev)
+        for i in range(4):
+            ops.decode_step(xs, w, cos, sin, ring.ring_k[0], ring.ring_v[0], 250 + i)
+    torch.cuda.synchronize()
+    assert ops.read_status(ops.default_status(dev)) == 0
+    print(f"profile case {which}: done")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
+    ap.add_argument("--profile-case", choices=["prefill", "decode"], help="run a small case for ncu and exit")
+    args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case)
+        return
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

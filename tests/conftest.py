@@ -38,14 +38,21 @@ def golden():
     return load_golden
 
 
-def regen_attention_layer(seed: int, b: int, t: int, hidden: int = 512, std: float = 0.02):
-    """Rebuild the seeded inputs of ``tests/golden/make_golden.py::attention_layer`` without the
-    reference: four bias-free Linear(hidden, hidden) constructed in q,k,v,o order (their default
-    init consumes the RNG), re-initialised N(0, std^2) in the same order, then x ~ N(0,1)."""
+def regen_projections(seed: int, hidden: int = 512, std: float = 0.02):
+    """Rebuild the seeded weights of ``tests/golden/make_golden.py`` without the reference: four
+    bias-free Linear(hidden, hidden) constructed in q,k,v,o order (their default init consumes the
+    RNG), re-initialised N(0, std^2) in the same order; q/k/v weights rounded to BF16-representable
+    values as the generator does for the full-size fixtures.  Leaves the RNG where x is drawn next."""
     torch.manual_seed(seed)
     lins = [torch.nn.Linear(hidden, hidden, bias=False) for _ in range(4)]
     for lin in lins:
         torch.nn.init.normal_(lin.weight, std=std)
-    x = torch.randn(b, t, hidden)
     wq, wk, wv, wo = (lin.weight.detach() for lin in lins)
+    return wq.bfloat16().float(), wk.bfloat16().float(), wv.bfloat16().float(), wo
+
+
+def regen_attention_layer(seed: int, b: int, t: int, hidden: int = 512, std: float = 0.02):
+    """Weights as ``regen_projections`` then x ~ N(0,1) rounded to BF16-representable values."""
+    wq, wk, wv, wo = regen_projections(seed, hidden, std)
+    x = torch.randn(b, t, hidden).bfloat16().float()
     return x, wq, wk, wv, wo

@@ -81,13 +81,24 @@ def long_band():
     save("band_T700.npz", seed=4, rows=rows, out=out[0, :, rows])
 
 
-def attention_layer(name, cfg, b, t, seed, rows=None, heads=None):
+def _round_bf16_(attn):
+    """Make the projection inputs BF16-representable (q/k/v weights; o_proj stays FP32) so that the
+    BF16 tensor-core path and the FP32 reference consume identical values."""
+    with torch.no_grad():
+        for lin in (attn.q_proj, attn.k_proj, attn.v_proj):
+            lin.weight.copy_(lin.weight.bfloat16().float())
+
+
+def attention_layer(name, cfg, b, t, seed, rows=None, bf16_inputs=False):
     """One reference MimiAttention layer, no cache: x -> (out after o_proj)."""
     torch.manual_seed(seed)
     attn = MimiAttention(cfg, 0, "sdpa").eval()
     for p in attn.parameters():
         torch.nn.init.normal_(p, std=0.02 if cfg.hidden_size == 512 else 0.2)
     x = torch.randn(b, t, cfg.hidden_size)
+    if bf16_inputs:
+        _round_bf16_(attn)
+        x = x.bfloat16().float()
     cos, sin = MimiRotaryEmbedding(cfg)(x, torch.arange(t)[None])
     mask = _attention_mask(batch_size=b, query_length=t, key_length=t, query_offset=0, key_offset=0,
                            sliding_window=cfg.sliding_window, padding_mask=None, backend="sdpa",
@@ -105,7 +116,7 @@ def attention_layer(name, cfg, b, t, seed, rows=None, heads=None):
     save(name, **arrays)
 
 
-def cached_streams(name, cfg, b, chunks, seed, keep_steps=None, std=0.2):
+def cached_streams(name, cfg, b, chunks, seed, keep_steps=None, std=0.2, bf16_inputs=False):
     """Reference MimiTransformerModel-style cached calls of ONE attention layer: the caller
     bookkeeping of model.py:2176-2206 (positions, mask sizes) followed by MimiAttention with a
     MimiKVCache.  ``chunks`` is the list of per-call frame counts."""
@@ -113,11 +124,15 @@ def cached_streams(name, cfg, b, chunks, seed, keep_steps=None, std=0.2):
     attn = MimiAttention(cfg, 0, "sdpa").eval()
     for p in attn.parameters():
         torch.nn.init.normal_(p, std=std)
+    if bf16_inputs:
+        _round_bf16_(attn)
     rope = MimiRotaryEmbedding(cfg)
     cache = MimiKVCache(1, sliding_window=cfg.sliding_window)
     xs, outs, seqs = [], [], []
     for step, t in enumerate(chunks):
         x = torch.randn(b, t, cfg.hidden_size)
+        if bf16_inputs:
+            x = x.bfloat16().float()
         past = cache.get_seq_length()
         pos = torch.arange(past, past + t)[None]
         k_len, k_off = cache.get_mask_sizes(t)
@@ -217,12 +232,12 @@ if __name__ == "__main__":
     long_band()
     attention_layer("tiny_attention_layer.npz", tiny_config(), 2, 21, seed=11)
     attention_layer("attention_layer_T250.npz", MimiConfig(), 2, 250, seed=1,
-                    rows=sorted(set(list(range(0, 250, 17)) + [127, 128, 249])))
+                    rows=sorted(set(list(range(0, 250, 17)) + [127, 128, 249])), bf16_inputs=True)
     attention_layer("attention_layer_T313.npz", MimiConfig(), 1, 313, seed=2,
-                    rows=sorted(set(list(range(0, 313, 23)) + [249, 250, 251, 312])))
+                    rows=sorted(set(list(range(0, 313, 23)) + [249, 250, 251, 312])), bf16_inputs=True)
     cached_streams("tiny_cached_chunks.npz", tiny_config(), 2, [4, 4, 4, 4, 4, 1, 1, 3, 9, 1], seed=12)
     cached_streams("tiny_cached_decode.npz", tiny_config(), 1, [1] * 12, seed=13)
     cached_streams("ring_decode_260.npz", MimiConfig(), 2, [1] * 260, seed=5, std=0.02,
-                   keep_steps={0, 1, 2, 127, 248, 249, 250, 251, 259})
+                   keep_steps={0, 1, 2, 127, 248, 249, 250, 251, 259}, bf16_inputs=True)
     transformer_stack_tiny()
     end_to_end_codes()

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from conftest import load_golden, regen_attention_layer
+from conftest import load_golden, regen_attention_layer, regen_projections
 from oracle import mimi_attention_oracle as O
 
 TOL = 2e-6   # FP32 reassociation noise between the oracle's eager softmax and the reference's SDPA
@@ -77,16 +77,12 @@ def test_tiny_cached_chunks_and_decode_match_reference():
 
 def test_ring_decode_260_matches_reference():
     g = load_golden("ring_decode_260.npz")
-    torch.manual_seed(int(g["seed"]))
-    lins = [torch.nn.Linear(512, 512, bias=False) for _ in range(4)]
-    for lin in lins:
-        torch.nn.init.normal_(lin.weight, std=0.02)
-    wq, wk, wv, wo = (lin.weight.detach() for lin in lins)
+    wq, wk, wv, wo = regen_projections(int(g["seed"]))
     cache = O.KVCacheOracle()
     keep = g["keep_steps"].tolist()
     got = []
     for step in range(260):
-        x = torch.randn(2, 1, 512)
+        x = torch.randn(2, 1, 512).bfloat16().float()
         out = O.attention_forward(x, wq, wk, wv, wo, cache=cache)
         if step in keep:
             got.append(out)
