@@ -27,7 +27,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 import torch
@@ -55,7 +54,8 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Streams SM clocks and throttle reasons from one `nvidia-smi -lms 50` child while the timed
+    region runs."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -64,36 +64,41 @@ class ClockSampler:
     def __init__(self, gpu_index: int) -> None:
         self.gpu_index = gpu_index
         self.samples: list[list[str]] = []
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self) -> None:
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                if out.returncode == 0 and out.stdout.strip():
-                    self.samples.append([c.strip() for c in out.stdout.strip().split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+        self.proc = None
 
     def __enter__(self):
-        self._thread.start()
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.15)     # let the first sample land before the timed region starts
+        except Exception:
+            self.proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        self._thread.join(timeout=6)
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        for line in out.splitlines():
+            cols = [c.strip() for c in line.split(",")]
+            if len(cols) == 7:
+                self.samples.append(cols)
 
     def summary(self) -> dict:
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        power = [float(s[2]) for s in self.samples if s[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(self.samples[0][1]),
-                "reasons": reasons, "samples": len(self.samples)}
+                "reasons": reasons, "samples": len(self.samples), "power_w_max": max(power) if power else None}
 
 
 # --------------------------------------------------------------------------- CPU oracle timing
@@ -392,7 +397,7 @@ def profile_case(which: str) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")

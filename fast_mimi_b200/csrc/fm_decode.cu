@@ -9,10 +9,10 @@
 // and softmax does not depend on slot order, so the visible set is identical.
 //
 // Work item = (stream, head): 2 x slots x 128 B of ring (K then V).  A persistent CTA streams items
-// through a 3-stage shared-memory ring with untiled TMA bulk copies issued by one producer thread
-// (192 KB in flight per SM); four consumer warps each take 64 slots: 16-byte vector reads, FP32
-// dot products, warp-shuffle reductions, and a four-way merge of (max, sum, output) through shared
-// memory.
+// through a 3-stage shared-memory ring with untiled TMA bulk copies issued by one producer thread.
+// Two consumer groups of four warps take alternate items, so two items are being reduced while a
+// third is in flight; inside a group each warp takes 64 slots: 16-byte vector reads, FP32 dot
+// products, warp-shuffle reductions, and a four-way merge of (max, sum, output) through shared memory.
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -21,17 +21,18 @@ namespace fm {
 namespace dec {
 constexpr int kMaxSlots = 256;
 constexpr int kStages = 3;
-constexpr int kWarps = 4;
-constexpr int kThreads = (kWarps + 1) * 32;
+constexpr int kWarps = 4;            // warps per consumer group
+constexpr int kGroups = 2;
+constexpr int kThreads = (kGroups * kWarps + 1) * 32;
 constexpr int kRowBytes = 128;
 
 struct Ctl {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   CtaCtl ctl;
-  float merge_m[2][kWarps];
-  float merge_l[2][kWarps];
-  float merge_o[2][kWarps][64];
+  float merge_m[kGroups][2][kWarps];
+  float merge_l[kGroups][2][kWarps];
+  float merge_o[kGroups][2][kWarps][64];
 };
 }  // namespace dec
 
@@ -68,7 +69,7 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
     return pos + 1 < ring_slots ? pos + 1 : ring_slots;   // slots 0..pos while filling, all once wrapped
   };
 
-  if (warp == kWarps) {
+  if (warp == kGroups * kWarps) {
     if (lane == 0) {
       int n = 0;
       for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
@@ -85,12 +86,16 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
   } else {
     const int chunk = lane & 7;    // which 8 of the 64 head dimensions this lane owns
     const int grp = lane >> 3;     // which of 4 consecutive slots
-    int n = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n) {
+    const int cg = warp / kWarps;  // consumer group: takes items cg, cg + kGroups, ...
+    const int gw = warp % kWarps;  // warp inside the group
+    const int gt = threadIdx.x - cg * kWarps * 32;
+    int n = cg;
+    for (long long item = blockIdx.x + static_cast<long long>(cg) * gridDim.x; item < n_items;
+         item += static_cast<long long>(kGroups) * gridDim.x, n += kGroups) {
       const int st = n % kStages;
       const uint32_t use = static_cast<uint32_t>(n / kStages);
-      const int nv = valid_slots(item);
-      const int s = item >> 3, h = item & 7;
+      const int nv = valid_slots(static_cast<int>(item));
+      const int s = static_cast<int>(item >> 3), h = static_cast<int>(item & 7);
       float qf[8];
       {
         const uint4 raw = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(s) * 512 + h * 64 + chunk * 8);
@@ -110,7 +115,7 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
       float m_w = -INFINITY;
 #pragma unroll
       for (int it = 0; it < 16; ++it) {
-        const int row = warp * 64 + it * 4 + grp;
+        const int row = gw * 64 + it * 4 + grp;
         float part = 0.f;
         if (row < nv) {
           const uint4 raw = *reinterpret_cast<const uint4*>(ks + row * kRowBytes + chunk * 16);
@@ -137,7 +142,7 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 #pragma unroll
       for (int it = 0; it < 16; ++it) {
-        const int row = warp * 64 + it * 4 + grp;
+        const int row = gw * 64 + it * 4 + grp;
         if (row < nv) {
           const float p = ex2_approx(sc[it] - m_use);
           l_w += p;
@@ -162,28 +167,28 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
         acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 8);
         acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
       }
-      const int mb = n & 1;
+      const int mb = (n / kGroups) & 1;
       if (grp == 0) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) c->merge_o[mb][warp][chunk * 8 + e] = acc[e];
+        for (int e = 0; e < 8; ++e) c->merge_o[cg][mb][gw][chunk * 8 + e] = acc[e];
         if (chunk == 0) {
-          c->merge_m[mb][warp] = m_w;
-          c->merge_l[mb][warp] = l_w;
+          c->merge_m[cg][mb][gw] = m_w;
+          c->merge_l[cg][mb][gw] = l_w;
         }
       }
-      named_bar_sync(1, kWarps * 32);
-      if (threadIdx.x < 64) {
+      named_bar_sync(1 + cg, kWarps * 32);
+      if (gt < 64) {
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, c->merge_m[mb][w]);
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, c->merge_m[cg][mb][w]);
         float num = 0.f, den = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-          const float f = ex2_approx(c->merge_m[mb][w] - mx);   // 0 for a warp that saw no slot
-          num = fmaf(f, c->merge_o[mb][w][threadIdx.x], num);
-          den = fmaf(f, c->merge_l[mb][w], den);
+          const float f = ex2_approx(c->merge_m[cg][mb][w] - mx);   // 0 for a warp that saw no slot
+          num = fmaf(f, c->merge_o[cg][mb][w][gt], num);
+          den = fmaf(f, c->merge_l[cg][mb][w], den);
         }
-        out[static_cast<size_t>(s) * 512 + h * 64 + threadIdx.x] = num / den;
+        out[static_cast<size_t>(s) * 512 + h * 64 + gt] = num / den;
       }
     }
   }

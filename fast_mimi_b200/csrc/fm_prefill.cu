@@ -167,10 +167,14 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       mbar_wait(&bars->s_full, static_cast<uint32_t>(jj) & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
 
+      // A 32-column group is skipped by the whole warp when none of the warp's 32 rows can see it.
+      const int warp_vis_lo = q0 + warp * 32 - window + 1 - k0;   // smallest visible column of any row
+      const int warp_vis_hi = q0 + warp * 32 + 31 - k0;           // largest
       // Pass 1: row maximum of the visible scores (log2 domain).
       float m_tile = -INFINITY;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
+        if (c0 > warp_vis_hi || c0 + 31 < warp_vis_lo) continue;
         uint32_t s[32];
         tmem_ld32(tmem_s + lane_sel + c0, s);
         tmem_ld_wait();
@@ -188,6 +192,14 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       float l_tile = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
+        uint8_t* half_base = (c0 >> 6) == 0 ? smem_kv + (2 * (jj % kKvStages)) * kTileBytes : smem_p_hi;
+        const int chunk0 = (c0 & 63) >> 3;   // first 16-byte chunk (8 keys) of this 32-key group
+        if (c0 > warp_vis_hi || c0 + 31 < warp_vis_lo) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+            *reinterpret_cast<uint4*>(half_base + sw128_offset(r, chunk0 + cc)) = make_uint4(0u, 0u, 0u, 0u);
+          continue;
+        }
         uint32_t s[32];
         tmem_ld32(tmem_s + lane_sel + c0, s);
         tmem_ld_wait();
@@ -202,12 +214,8 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             p[e] = ex2_approx(x);
           }
           pk[c / 2] = Pack16<VT>::pack(p[0], p[1]);
-          // Sum what the MMA will actually see, so numerator and denominator round alike.
-          const float2 back = Pack16<VT>::unpack(pk[c / 2]);
-          l_tile += back.x + back.y;
+          l_tile += p[0] + p[1];
         }
-        uint8_t* half_base = (c0 >> 6) == 0 ? smem_kv + (2 * (jj % kKvStages)) * kTileBytes : smem_p_hi;
-        const int chunk0 = (c0 & 63) >> 3;   // first 16-byte chunk (8 keys) of this 32-key group
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           *reinterpret_cast<uint4*>(half_base + sw128_offset(r, chunk0 + cc)) =

@@ -140,8 +140,22 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     const bool row_ok = row < M;
     const int clip = row_ok ? static_cast<int>(row / ep.T) : 0;
     const int t = row_ok ? static_cast<int>(row % ep.T) : 0;
-    const float* cos_row = ep.cos + clip * ep.cos_bstride + static_cast<long long>(t) * 64;
-    const float* sin_row = ep.sin + clip * ep.cos_bstride + static_cast<long long>(t) * 64;
+    // RoPE factors of this thread's frame, kept in registers for all heads of q and k.  The table's two
+    // 32-wide halves are identical by construction (frequencies repeated), so only the first is read.
+    float rc[32], rs[32];
+    if (n_first < 4 && row_ok) {
+      const float4* c4 = reinterpret_cast<const float4*>(ep.cos + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
+      const float4* s4 = reinterpret_cast<const float4*>(ep.sin + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 c = __ldg(c4 + i), sn = __ldg(s4 + i);
+        rc[4 * i] = c.x; rc[4 * i + 1] = c.y; rc[4 * i + 2] = c.z; rc[4 * i + 3] = c.w;
+        rs[4 * i] = sn.x; rs[4 * i + 1] = sn.y; rs[4 * i + 2] = sn.z; rs[4 * i + 3] = sn.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { rc[i] = 1.f; rs[i] = 0.f; }
+    }
     long long ring_row = -1;
     if (ep.ring_k != nullptr && row_ok) {
       const int pos = ep.pos_base + (ep.clip_pos != nullptr ? ep.clip_pos[clip] : 0) + t;
@@ -156,52 +170,55 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
+      uint16_t* lin = seg == 0 ? ep.q : (seg == 1 ? ep.k : ep.v);
+      uint16_t* ring = seg == 1 ? ep.ring_k : (seg == 2 ? ep.ring_v : nullptr);
 #pragma unroll 1
       for (int hh = 0; hh < 4; ++hh) {
         const int head = (ntile & 1) * 4 + hh;
-        uint32_t lo[32], hi[32];
-        tmem_ld32(t_row + hh * 64, lo);
-        tmem_ld32(t_row + hh * 64 + 32, hi);
-        tmem_ld_wait();
-        uint32_t packed[32];
-        if (seg < 2) {
+        uint4* lin_dst = (lin != nullptr && row_ok) ? reinterpret_cast<uint4*>(lin + row * 512 + head * 64) : nullptr;
+        uint4* ring_dst = (ring != nullptr && ring_row >= 0)
+                              ? reinterpret_cast<uint4*>(ring + (ring_row + static_cast<long long>(head) * ep.ring_slots) * 64)
+                              : nullptr;
 #pragma unroll
-          for (int d = 0; d < 32; d += 2) {
-            float o_lo[2], o_hi[2];
+        for (int piece = 0; piece < 2; ++piece) {
+          // 16 columns of the head's first half and the 16 columns 32 further on: a RoPE pair set.
+          uint32_t lo[16], hi[16];
+          tmem_ld16(t_row + hh * 64 + piece * 16, lo);
+          tmem_ld16(t_row + hh * 64 + 32 + piece * 16, hi);
+          tmem_ld_wait();
+          uint32_t plo[8], phi[8];
+          if (seg < 2) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float a = __uint_as_float(lo[d + e]), b = __uint_as_float(hi[d + e]);
-              const float c0 = row_ok ? __ldg(cos_row + d + e) : 1.f, s0 = row_ok ? __ldg(sin_row + d + e) : 0.f;
-              const float c1 = row_ok ? __ldg(cos_row + 32 + d + e) : 1.f,
-                          s1 = row_ok ? __ldg(sin_row + 32 + d + e) : 0.f;
-              o_lo[e] = a * c0 - b * s0;
-              o_hi[e] = b * c1 + a * s1;
+            for (int d = 0; d < 16; d += 2) {
+              float o_lo[2], o_hi[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float a = __uint_as_float(lo[d + e]), b = __uint_as_float(hi[d + e]);
+                const float c = rc[piece * 16 + d + e], sn = rs[piece * 16 + d + e];
+                o_lo[e] = a * c - b * sn;
+                o_hi[e] = b * c + a * sn;
+              }
+              plo[d / 2] = Pack16<__nv_bfloat16>::pack(o_lo[0], o_lo[1]);
+              phi[d / 2] = Pack16<__nv_bfloat16>::pack(o_hi[0], o_hi[1]);
             }
-            packed[d / 2] = Pack16<__nv_bfloat16>::pack(o_lo[0], o_lo[1]);
-            packed[16 + d / 2] = Pack16<__nv_bfloat16>::pack(o_hi[0], o_hi[1]);
-          }
-        } else {
+          } else {
 #pragma unroll
-          for (int d = 0; d < 32; d += 2) {
-            packed[d / 2] = Pack16<VT>::pack(__uint_as_float(lo[d]), __uint_as_float(lo[d + 1]));
-            packed[16 + d / 2] = Pack16<VT>::pack(__uint_as_float(hi[d]), __uint_as_float(hi[d + 1]));
+            for (int d = 0; d < 16; d += 2) {
+              plo[d / 2] = Pack16<VT>::pack(__uint_as_float(lo[d]), __uint_as_float(lo[d + 1]));
+              phi[d / 2] = Pack16<VT>::pack(__uint_as_float(hi[d]), __uint_as_float(hi[d + 1]));
+            }
           }
-        }
-        if (row_ok) {
-          uint16_t* lin = seg == 0 ? ep.q : (seg == 1 ? ep.k : ep.v);
-          if (lin != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(lin + row * 512 + head * 64);
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          if (lin_dst != nullptr) {
+            lin_dst[piece * 2] = make_uint4(plo[0], plo[1], plo[2], plo[3]);
+            lin_dst[piece * 2 + 1] = make_uint4(plo[4], plo[5], plo[6], plo[7]);
+            lin_dst[4 + piece * 2] = make_uint4(phi[0], phi[1], phi[2], phi[3]);
+            lin_dst[4 + piece * 2 + 1] = make_uint4(phi[4], phi[5], phi[6], phi[7]);
           }
-          if (seg > 0 && ring_row >= 0) {
-            uint16_t* ring = seg == 1 ? ep.ring_k : ep.ring_v;
-            uint4* dst = reinterpret_cast<uint4*>(
-                ring + (ring_row + static_cast<long long>(head) * ep.ring_slots) * 64);
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              dst[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          if (ring_dst != nullptr) {
+            ring_dst[piece * 2] = make_uint4(plo[0], plo[1], plo[2], plo[3]);
+            ring_dst[piece * 2 + 1] = make_uint4(plo[4], plo[5], plo[6], plo[7]);
+            ring_dst[4 + piece * 2] = make_uint4(phi[0], phi[1], phi[2], phi[3]);
+            ring_dst[4 + piece * 2 + 1] = make_uint4(phi[4], phi[5], phi[6], phi[7]);
           }
         }
       }

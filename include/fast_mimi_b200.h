@@ -30,7 +30,9 @@ int fm_abi_version(void);
  * Replaces q_proj/k_proj/v_proj + _apply_rope (src/fast_mimi/model.py:1897-1912; packed-weight form
  * src/fast_mimi/_packed_qkv.py:139-171).
  *   x      [B*T, 512] BF16          w_qkv [1536, 512] BF16 = cat(Wq, Wk, Wv) rows
- *   cos,sin [1 or B, T, 64] FP32 (the reference's position_embeddings); cos_bstride = 0 or T*64
+ *   cos,sin [1 or B, T, 64] FP32 (the reference's position_embeddings); cos_bstride = 0 or T*64.
+ *           Columns 32..63 repeat columns 0..31 (MimiRotaryEmbedding builds them so,
+ *           src/fast_mimi/model.py:1533); the kernel reads the first 32.
  *   q,k    [B*T, 512] BF16 out      v [B*T, 512] value_dtype out */
 int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
                      long long cos_bstride, void* q, void* k, void* v, int B, int T, int value_dtype,
