@@ -6,57 +6,66 @@
 // Replaces the three bias-free projections plus _apply_rope of the reference
 // (src/fast_mimi/model.py:1897-1912; packed form src/fast_mimi/_packed_qkv.py:139-171).
 //
-// One CTA owns a 128-frame tile of x.  The x tile (128 x 512 BF16 = 128 KB) is loaded once by
-// TMA and stays in shared memory; W_qkv streams through a 3-stage ring of 256x64 tiles (it is
-// 1.5 MB and lives in L2).  Each 128x256 output tile (4 heads of q, k or v) is accumulated by
-// tcgen05.mma into one of two 256-column TMEM buffers, so the epilogue of tile n overlaps the
-// MMAs of tile n+1.  Warps 0-3: epilogue (thread = one frame row; both halves of a RoPE pair are
-// in that thread's TMEM row).  Warp 4: TMA producer.  Warp 5: MMA issuer.
+// Two CTAs on neighbouring SMs work as a pair (cluster of 2, tcgen05 cta_group::2).  Each CTA owns a
+// 128-frame tile of x, loaded once by TMA and kept in shared memory (128 KB), and loads HALF of every
+// 256x64 W_qkv tile (128 weight rows); one tcgen05.mma issued by the pair's leader multiplies the
+// 256 frames of both CTAs by all 256 weight rows, so each W byte is fetched from L2 once per 256 frames.
+// Each CTA's 128x256 FP32 result lands in its own TMEM (two 256-column buffers: the epilogue of output
+// tile n overlaps the MMAs of tile n+1).  Epilogue warps read one frame row per thread (both halves of
+// a RoPE pair sit in the same row), rotate, round, stage 32x64 slabs in swizzled shared memory and write
+// them with TMA stores (full 128-byte lines).  Warps 0-3: epilogue.  Warp 4: TMA producer (+ TMEM
+// allocation).  Warp 5: MMA issuer (leader CTA only).
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
 namespace fm {
 
 namespace gemm {
-constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
+constexpr int kBlockM = 128;           // frames per CTA
+constexpr int kBlockN = 256;           // outputs per tile (4 heads of q, k or v)
+constexpr int kHalfN = kBlockN / 2;    // weight rows loaded by each CTA of the pair
 constexpr int kBlockK = 64;            // one 128-byte swizzle row of BF16
 constexpr int kHidden = 512;           // K
 constexpr int kKChunks = kHidden / kBlockK;
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB per K chunk
-constexpr int kBBytes = kBlockN * kBlockK * 2;   // 32 KB per stage
+constexpr int kBBytes = kHalfN * kBlockK * 2;    // 16 KB per stage per CTA
+constexpr int kSlabBytes = 32 * 128;             // one warp's 32 frames x 64 outputs x 16 bit
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = 1024 /*align*/ + kKChunks * kABytes + kStages * kBBytes + 256 /*barriers*/;
+constexpr int kSmemBytes = 1024 /*align*/ + kKChunks * kABytes + kStages * kBBytes + 4 * 2 * kSlabBytes + 256;
 
 struct Barriers {
-  uint64_t a_full[kKChunks];
-  uint64_t b_full[kStages];
-  uint64_t b_empty[kStages];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t a_full[kKChunks];   // used in the leader: bytes of both CTAs' x chunks
+  uint64_t b_full[kStages];    // used in the leader: bytes of both halves of a W tile
+  uint64_t b_empty[kStages];   // per CTA: stage consumed by the tensor core
+  uint64_t acc_full[2];        // per CTA: accumulator buffer complete
+  uint64_t acc_empty[2];       // used in the leader: 8 epilogue warps (4 per CTA) drained the buffer
   uint32_t tmem_base;
+  uint32_t skip;               // leader's view of "status already non-zero at start"
   CtaCtl ctl;
 };
 static_assert(sizeof(Barriers) <= 256, "barrier block too large");
 }  // namespace gemm
 
 template <typename VT>
-__global__ void __launch_bounds__(gemm::kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm::kThreads, 1)
 qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                     QkvEpilogueArgs ep, int M, int n_tiles_per_cta, int* status) {
+                     const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, QkvEpilogueArgs ep, int M, int n_tiles_per_cta,
+                     int* status) {
   using namespace gemm;
-  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;                                   // kKChunks x [128 rows x 128 B]
-  uint8_t* smem_b = smem + kKChunks * kABytes;              // kStages  x [256 rows x 128 B]
-  Barriers* bars = reinterpret_cast<Barriers*>(smem_b + kStages * kBBytes);
+  uint8_t* smem_b = smem_a + kKChunks * kABytes;            // kStages  x [128 rows x 128 B]
+  uint8_t* smem_out = smem_b + kStages * kBBytes;           // 4 warps x 2 x [32 rows x 128 B]
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_out + 4 * 2 * kSlabBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();      // 0 = pair leader
+  const bool leader = rank == 0;
   const int m0 = blockIdx.x * kBlockM;
   const int n_first = blockIdx.y * n_tiles_per_cta;
 
@@ -68,46 +77,52 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->acc_full[i], 1);
-      mbar_init(&bars->acc_empty[i], 4);
+      mbar_init(&bars->acc_empty[i], 8);
     }
     bars->ctl.abort = 0;
+    bars->skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1u : 0u;
     fence_mbar_init();
   }
   if (warp == 4) {
-    tmem_alloc(&bars->tmem_base, kTmemCols);
-    tmem_relinquish();
+    tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
   }
   tc_fence_before_sync();
   __syncthreads();
+  cluster_sync_all();            // both CTAs' barriers exist before anything signals across the pair
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   CtaCtl* ctl = &bars->ctl;
+  // Both CTAs take the leader's decision, so the pair stays in step.
+  const bool skip = ld_shared_cluster_u32(map_to_cta(smem_u32(&bars->skip), 0)) != 0;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------ TMA producer
+  if (skip) {
+    // a previous kernel already reported a timeout through this status word: do nothing
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer (one per CTA)
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
       tma_prefetch_desc(&tmap_w);
       for (int kc = 0; kc < kKChunks; ++kc) {
-        mbar_arrive_expect_tx(&bars->a_full[kc], kABytes);
-        tma_load_2d(smem_a + kc * kABytes, &tmap_x, &bars->a_full[kc], kc * kBlockK, m0);
+        if (leader) mbar_arrive_expect_tx(&bars->a_full[kc], 2 * kABytes);
+        tma_load_2d_pair(smem_a + kc * kABytes, &tmap_x, &bars->a_full[kc], kc * kBlockK, m0);
       }
       int stage = 0;
       uint32_t phase = 0;
       for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
-        const int n0 = (n_first + nt) * kBlockN;
+        const int n0 = (n_first + nt) * kBlockN + static_cast<int>(rank) * kHalfN;
         for (int kc = 0; kc < kKChunks; ++kc) {
           mbar_wait(&bars->b_empty[stage], phase ^ 1u, ctl, status, kErrWaitConsumer);
-          mbar_arrive_expect_tx(&bars->b_full[stage], kBBytes);
-          tma_load_2d(smem_b + stage * kBBytes, &tmap_w, &bars->b_full[stage], kc * kBlockK, n0);
+          if (leader) mbar_arrive_expect_tx(&bars->b_full[stage], 2 * kBBytes);
+          tma_load_2d_pair(smem_b + stage * kBBytes, &tmap_w, &bars->b_full[stage], kc * kBlockK, n0);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 5) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(kBlockM, kBlockN, 1, 1, 0, 0);
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, 1, 1, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
       for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
@@ -125,16 +140,16 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 #pragma unroll
           for (int ks = 0; ks < kBlockK / 16; ++ks) {
             // +32 bytes per 16-element K step inside the 128-byte swizzle row (encoded >> 4).
-            tc_mma_ss(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
+            tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
           }
-          tc_commit(&bars->b_empty[stage]);
+          tc_commit_pair(&bars->b_empty[stage], 3);     // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        tc_commit(&bars->acc_full[buf]);
+        tc_commit_pair(&bars->acc_full[buf], 3);        // both CTAs' epilogues may read their TMEM
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 0..3)
+    // ------------------------------------------------------------ epilogue (warps 0..3 of both CTAs)
     const int row_in_tile = warp * 32 + lane;
     const long long row = static_cast<long long>(m0) + row_in_tile;
     const bool row_ok = row < M;
@@ -162,6 +177,9 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       // Only the newest ring_slots frames of a clip land in the ring.
       if (t >= ep.T - ep.ring_slots) ring_row = static_cast<long long>(clip) * 8 * ep.ring_slots + pos % ep.ring_slots;
     }
+    const uint32_t acc_empty_leader = map_to_cta(smem_u32(&bars->acc_empty[0]), 0);
+    uint8_t* slab0 = smem_out + warp * 2 * kSlabBytes;
+    int slab_turn = 0;
     for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
       const int buf = nt & 1;
       const uint32_t use = static_cast<uint32_t>(nt >> 1);
@@ -170,12 +188,18 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
-      uint16_t* lin = seg == 0 ? ep.q : (seg == 1 ? ep.k : ep.v);
+      const CUtensorMap* omap = seg == 0 ? &tmap_q : (seg == 1 ? &tmap_k : &tmap_v);
+      const bool lin_ok = (seg == 0 ? ep.q : (seg == 1 ? ep.k : ep.v)) != nullptr;
       uint16_t* ring = seg == 1 ? ep.ring_k : (seg == 2 ? ep.ring_v : nullptr);
 #pragma unroll 1
       for (int hh = 0; hh < 4; ++hh) {
         const int head = (ntile & 1) * 4 + hh;
-        uint4* lin_dst = (lin != nullptr && row_ok) ? reinterpret_cast<uint4*>(lin + row * 512 + head * 64) : nullptr;
+        uint8_t* slab = slab0 + (slab_turn & 1) * kSlabBytes;
+        if (lin_ok) {
+          // The store that last read this slab (two heads ago) must be done with it.
+          if (lane == 0) bulk_wait_group_read<1>();
+          __syncwarp();
+        }
         uint4* ring_dst = (ring != nullptr && ring_row >= 0)
                               ? reinterpret_cast<uint4*>(ring + (ring_row + static_cast<long long>(head) * ep.ring_slots) * 64)
                               : nullptr;
@@ -208,11 +232,12 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
               phi[d / 2] = Pack16<VT>::pack(__uint_as_float(hi[d]), __uint_as_float(hi[d + 1]));
             }
           }
-          if (lin_dst != nullptr) {
-            lin_dst[piece * 2] = make_uint4(plo[0], plo[1], plo[2], plo[3]);
-            lin_dst[piece * 2 + 1] = make_uint4(plo[4], plo[5], plo[6], plo[7]);
-            lin_dst[4 + piece * 2] = make_uint4(phi[0], phi[1], phi[2], phi[3]);
-            lin_dst[4 + piece * 2 + 1] = make_uint4(phi[4], phi[5], phi[6], phi[7]);
+          if (lin_ok) {
+            // Row `lane` of the slab, 16-byte chunks 2p, 2p+1 (first half) and 4+2p, 4+2p+1 (second half).
+            *reinterpret_cast<uint4*>(slab + sw128_offset(lane, piece * 2)) = make_uint4(plo[0], plo[1], plo[2], plo[3]);
+            *reinterpret_cast<uint4*>(slab + sw128_offset(lane, piece * 2 + 1)) = make_uint4(plo[4], plo[5], plo[6], plo[7]);
+            *reinterpret_cast<uint4*>(slab + sw128_offset(lane, 4 + piece * 2)) = make_uint4(phi[0], phi[1], phi[2], phi[3]);
+            *reinterpret_cast<uint4*>(slab + sw128_offset(lane, 4 + piece * 2 + 1)) = make_uint4(phi[4], phi[5], phi[6], phi[7]);
           }
           if (ring_dst != nullptr) {
             ring_dst[piece * 2] = make_uint4(plo[0], plo[1], plo[2], plo[3]);
@@ -221,29 +246,37 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
             ring_dst[4 + piece * 2 + 1] = make_uint4(phi[4], phi[5], phi[6], phi[7]);
           }
         }
+        if (lin_ok) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            // Rows past M are clipped by the tensor map.
+            tma_store_2d(omap, slab, head * 64, m0 + warp * 32);
+            bulk_commit_group();
+          }
+          ++slab_turn;
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
     }
+    if (lane == 0) bulk_wait_group_read<0>();
   }
 
-  // Teardown: every thread arrives here; the allocating warp releases tensor memory.
+  // Teardown: neither CTA may leave (or release TMEM) while its partner can still signal it.
   tc_fence_before_sync();
   __syncthreads();
-  if (ctl->abort) {
-    // Give copies that may still be in flight time to land before shared memory is reused.
-    __nanosleep(20000);
-  }
+  if (ctl->abort) __nanosleep(20000);   // copies that may still be in flight get time to land
+  cluster_sync_all();
   if (warp == 4) {
-    __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
-static int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                          uint32_t box_cols) {
+static int encode_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                           uint32_t box_cols) {
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {cols * 2};
   const cuuint32_t box[2] = {box_cols, box_rows};
@@ -257,21 +290,33 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
   using namespace gemm;
   if (M <= 0) return M == 0 ? 0 : -1;
   if (ep.T <= 0 || ep.cos == nullptr || ep.sin == nullptr) return -1;
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_qkv)) & 15u) return -3;
-  CUtensorMap tmap_x, tmap_w;
-  int rc = encode_2d_bf16(&tmap_x, x, static_cast<uint64_t>(M), kHidden, kBlockM, kBlockK);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_qkv) | reinterpret_cast<uintptr_t>(ep.q) |
+       reinterpret_cast<uintptr_t>(ep.k) | reinterpret_cast<uintptr_t>(ep.v) | reinterpret_cast<uintptr_t>(ep.ring_k) |
+       reinterpret_cast<uintptr_t>(ep.ring_v)) & 15u)
+    return -3;
+  CUtensorMap tmap_x, tmap_w, tmap_q, tmap_k, tmap_v;
+  int rc = encode_2d_16bit(&tmap_x, x, static_cast<uint64_t>(M), kHidden, kBlockM, kBlockK);
   if (rc != 0) return rc;
-  rc = encode_2d_bf16(&tmap_w, w_qkv, 1536, kHidden, kBlockN, kBlockK);
+  rc = encode_2d_16bit(&tmap_w, w_qkv, 1536, kHidden, kHalfN, kBlockK);
+  if (rc != 0) return rc;
+  // Output maps (16-bit elements whatever the float format); a missing output reuses x as a placeholder
+  // that the kernel never stores through.
+  rc = encode_2d_16bit(&tmap_q, ep.q != nullptr ? ep.q : x, static_cast<uint64_t>(M), 512, 32, 64);
+  if (rc != 0) return rc;
+  rc = encode_2d_16bit(&tmap_k, ep.k != nullptr ? ep.k : x, static_cast<uint64_t>(M), 512, 32, 64);
+  if (rc != 0) return rc;
+  rc = encode_2d_16bit(&tmap_v, ep.v != nullptr ? ep.v : x, static_cast<uint64_t>(M), 512, 32, 64);
   if (rc != 0) return rc;
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
-  // Few frame tiles (streaming decode): split the six 256-wide output tiles over CTAs too.
-  const int n_split = m_tiles >= 148 ? 1 : (m_tiles >= 50 ? 3 : 6);
+  const int m_ctas = (m_tiles + 1) & ~1;   // CTAs come in pairs; an odd last tile gets an idle partner
+  // Few frame tiles (streaming decode): split the six 256-wide output tiles over CTA pairs too.
+  const int n_split = m_ctas >= 148 ? 1 : (m_ctas >= 50 ? 3 : 6);
   const int per_cta = 6 / n_split;
-  dim3 grid(m_tiles, n_split);
+  dim3 grid(m_ctas, n_split);
   auto kern = value_is_fp16 ? qkv_rope_gemm_kernel<__half> : qkv_rope_gemm_kernel<__nv_bfloat16>;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (rc != 0) return rc;
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, ep, M, per_cta, status);
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, tmap_q, tmap_k, tmap_v, ep, M, per_cta, status);
   return static_cast<int>(cudaGetLastError());
 }
 
