@@ -13,8 +13,8 @@
 // Each CTA's 128x256 FP32 result lands in its own TMEM (two 256-column buffers: the epilogue of output
 // tile n overlaps the MMAs of tile n+1).  Epilogue warps read one frame row per thread (both halves of
 // a RoPE pair sit in the same row), rotate, round, stage 32x64 slabs in swizzled shared memory and write
-// them with TMA stores (full 128-byte lines).  Warps 0-3: epilogue.  Warp 4: TMA producer (+ TMEM
-// allocation).  Warp 5: MMA issuer (leader CTA only).
+// them with TMA stores (full 128-byte lines).  Warps 0-7: epilogue (two per TMEM lane group, two heads
+// each).  Warp 8: TMA producer (+ TMEM allocation).  Warp 9: MMA issuer (leader CTA only).
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -31,16 +31,17 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB per K chunk
 constexpr int kBBytes = kHalfN * kBlockK * 2;    // 16 KB per stage per CTA
 constexpr int kSlabBytes = 32 * 128;             // one warp's 32 frames x 64 outputs x 16 bit
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;                     // two per TMEM lane group: heads 0,1 and heads 2,3 of a tile
+constexpr int kThreads = (kEpiWarps + 2) * 32;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = 1024 /*align*/ + kKChunks * kABytes + kStages * kBBytes + 4 * 2 * kSlabBytes + 256;
+constexpr int kSmemBytes = 1024 /*align*/ + kKChunks * kABytes + kStages * kBBytes + kEpiWarps * kSlabBytes + 256;
 
 struct Barriers {
   uint64_t a_full[kKChunks];   // used in the leader: bytes of both CTAs' x chunks
   uint64_t b_full[kStages];    // used in the leader: bytes of both halves of a W tile
   uint64_t b_empty[kStages];   // per CTA: stage consumed by the tensor core
   uint64_t acc_full[2];        // per CTA: accumulator buffer complete
-  uint64_t acc_empty[2];       // used in the leader: 8 epilogue warps (4 per CTA) drained the buffer
+  uint64_t acc_empty[2];       // used in the leader: 16 epilogue warps (8 per CTA) drained the buffer
   uint32_t tmem_base;
   uint32_t skip;               // leader's view of "status already non-zero at start"
   CtaCtl ctl;
@@ -59,8 +60,8 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;                                   // kKChunks x [128 rows x 128 B]
   uint8_t* smem_b = smem_a + kKChunks * kABytes;            // kStages  x [128 rows x 128 B]
-  uint8_t* smem_out = smem_b + kStages * kBBytes;           // 4 warps x 2 x [32 rows x 128 B]
-  Barriers* bars = reinterpret_cast<Barriers*>(smem_out + 4 * 2 * kSlabBytes);
+  uint8_t* smem_out = smem_b + kStages * kBBytes;           // kEpiWarps x [32 rows x 128 B]
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_out + kEpiWarps * kSlabBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,13 +78,13 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->acc_full[i], 1);
-      mbar_init(&bars->acc_empty[i], 8);
+      mbar_init(&bars->acc_empty[i], 2 * kEpiWarps);
     }
     bars->ctl.abort = 0;
     bars->skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1u : 0u;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == kEpiWarps) {
     tmem_alloc_pair(&bars->tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
@@ -98,7 +99,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 
   if (skip) {
     // a previous kernel already reported a timeout through this status word: do nothing
-  } else if (warp == 4) {
+  } else if (warp == kEpiWarps) {
     // ------------------------------------------------------------ TMA producer (one per CTA)
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
@@ -119,7 +120,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kEpiWarps + 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, 1, 1, 0, 0);
@@ -149,8 +150,10 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 0..3 of both CTAs)
-    const int row_in_tile = warp * 32 + lane;
+    // ------------------------------------------------------------ epilogue (warps 0..7 of both CTAs)
+    const int lg = warp & 3;      // TMEM lane group: frames 32*lg .. 32*lg+31 of the tile
+    const int hsel = warp >> 2;   // which two of the tile's four heads this warp handles
+    const int row_in_tile = lg * 32 + lane;
     const long long row = static_cast<long long>(m0) + row_in_tile;
     const bool row_ok = row < M;
     const int clip = row_ok ? static_cast<int>(row / ep.T) : 0;
@@ -178,8 +181,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       if (t >= ep.T - ep.ring_slots) ring_row = static_cast<long long>(clip) * 8 * ep.ring_slots + pos % ep.ring_slots;
     }
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(&bars->acc_empty[0]), 0);
-    uint8_t* slab0 = smem_out + warp * 2 * kSlabBytes;
-    int slab_turn = 0;
+    uint8_t* slab = smem_out + warp * kSlabBytes;
     for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
       const int buf = nt & 1;
       const uint32_t use = static_cast<uint32_t>(nt >> 1);
@@ -187,17 +189,16 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       const int seg = ntile >> 1;              // 0 = q, 1 = k, 2 = v
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
       const CUtensorMap* omap = seg == 0 ? &tmap_q : (seg == 1 ? &tmap_k : &tmap_v);
       const bool lin_ok = (seg == 0 ? ep.q : (seg == 1 ? ep.k : ep.v)) != nullptr;
       uint16_t* ring = seg == 1 ? ep.ring_k : (seg == 2 ? ep.ring_v : nullptr);
 #pragma unroll 1
-      for (int hh = 0; hh < 4; ++hh) {
+      for (int hh = hsel * 2; hh < hsel * 2 + 2; ++hh) {
         const int head = (ntile & 1) * 4 + hh;
-        uint8_t* slab = slab0 + (slab_turn & 1) * kSlabBytes;
         if (lin_ok) {
-          // The store that last read this slab (two heads ago) must be done with it.
-          if (lane == 0) bulk_wait_group_read<1>();
+          // The previous store out of this warp's slab must have finished reading it.
+          if (lane == 0) bulk_wait_group_read<0>();
           __syncwarp();
         }
         uint4* ring_dst = (ring != nullptr && ring_row >= 0)
@@ -251,10 +252,9 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
           __syncwarp();
           if (lane == 0) {
             // Rows past M are clipped by the tensor map.
-            tma_store_2d(omap, slab, head * 64, m0 + warp * 32);
+            tma_store_2d(omap, slab, head * 64, m0 + lg * 32);
             bulk_commit_group();
           }
-          ++slab_turn;
         }
       }
       tc_fence_before_sync();
@@ -269,7 +269,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   __syncthreads();
   if (ctl->abort) __nanosleep(20000);   // copies that may still be in flight get time to land
   cluster_sync_all();
-  if (warp == 4) {
+  if (warp == kEpiWarps) {
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
