@@ -279,9 +279,6 @@ static int encode_clip_tile(CUtensorMap* map, const void* base, int B, int T, CU
   return encode_tiled(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-int launch_band_attn_clip(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* out, int B, int T,
-                          int window, float scale, int value_is_fp16, int* status, cudaStream_t st);
-
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st) {
   using namespace fmha;
@@ -290,6 +287,9 @@ int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* 
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(out)) & 15u)
     return -3;
+  // Clips that fit two 128-frame tiles take the whole-clip kernel (one CTA per (clip, head) item).
+  if (T > kTile && T <= 2 * kTile && B <= (1 << 27))
+    return launch_band_attn_clip(q, k, v, out, B, T, window, scale, value_is_fp16, status, st);
   CUtensorMap tq, tk, tv;
   int rc = encode_clip_tile(&tq, q, B, T, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
   if (rc != 0) return rc;
@@ -297,304 +297,12 @@ int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* 
   if (rc != 0) return rc;
   rc = encode_clip_tile(&tv, v, B, T, value_is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
   if (rc != 0) return rc;
-  // Clips that fit two 128-frame tiles take the whole-clip kernel (one CTA per (clip, head) item).
-  if (T > kTile && T <= 2 * kTile && B <= (1 << 27))
-    return launch_band_attn_clip(tq, tk, tv, out, B, T, window, scale, value_is_fp16, status, st);
   auto kern = value_is_fp16 ? band_attn_prefill_kernel<__half> : band_attn_prefill_kernel<__nv_bfloat16>;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (rc != 0) return rc;
   dim3 grid((T + kTile - 1) / kTile, 8, B);
   const float scale_log2e = scale * 1.4426950408889634f;
   kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, static_cast<uint16_t*>(out), T, window, scale_log2e, status);
-  return static_cast<int>(cudaGetLastError());
-}
-
-
-// ---------------------------------------------------------------------------------------------------
-// Whole-clip variant for 128 < T <= 256 frames (Mimi's 10 s clips: T = 250).
-//
-// A persistent CTA takes (clip, head) items.  All of an item's operands — Q, K, V for both 128-frame
-// halves, 96 KB — arrive in one TMA batch, and the next item's batch is in flight while the current one
-// is computed (two 96 KB buffers).  The three score tiles of the causal band (rows 0-127 x keys 0-127,
-// rows 128-255 x keys 0-127 and x keys 128-255) are issued back to back into 384 TMEM columns, so every
-// softmax row sees its complete set of scores at once: one pass for the row maximum, one for the
-// probabilities, no running rescale, and the tensor core accumulates P V for both key tiles directly in
-// TMEM.  P tiles overwrite the item's dead Q/K buffers (plus one 32 KB extra tile).  Warps 0-3: rows
-// 0-127.  Warps 4-7: rows 128-255.  Warp 8: TMA + MMA issue.
-namespace clip {
-constexpr int kTile = 128;
-constexpr int kD = 64;
-constexpr int kTileBytes = kTile * kD * 2;
-constexpr int kItemBytes = 6 * kTileBytes;          // Q0 Q1 K0 K1 V0 V1
-constexpr int kThreads = 9 * 32;
-constexpr int kTmemCols = 512;                      // S00 | S10 | S11 | O0 | O1
-constexpr int kSmemBytes = 1024 + 2 * kItemBytes + 2 * kTileBytes + 256;
-
-struct Barriers {
-  uint64_t load_full[2];
-  uint64_t buf_free[2];
-  uint64_t s_full;
-  uint64_t p_full[2];
-  uint64_t o_full[2];
-  uint32_t tmem_base;
-  CtaCtl ctl;
-};
-static_assert(sizeof(Barriers) <= 256, "barrier block too large");
-}  // namespace clip
-
-template <typename VT>
-__global__ void __launch_bounds__(clip::kThreads, 1)
-band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                      const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ out, int n_items, int T,
-                      int window, float scale_log2e, int* status) {
-  using namespace clip;
-  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_p11 = smem + 2 * kItemBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(smem_p11 + 2 * kTileBytes);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->load_full[i], 1);
-      mbar_init(&bars->buf_free[i], 1);
-      mbar_init(&bars->p_full[i], 4);
-      mbar_init(&bars->o_full[i], 1);
-    }
-    mbar_init(&bars->s_full, 1);
-    bars->ctl.abort = 0;
-    fence_mbar_init();
-  }
-  if (warp == 8) {
-    tmem_alloc(&bars->tmem_base, kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-  CtaCtl* ctl = &bars->ctl;
-  const int n_local = (n_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-
-  if (warp == 8) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
-      auto load_item = [&](int n) {
-        const int item = blockIdx.x + n * gridDim.x;
-        const int c = item >> 3, h = item & 7, b = n & 1;
-        uint8_t* base = smem + b * kItemBytes;
-        mbar_arrive_expect_tx(&bars->load_full[b], kItemBytes);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tma_load_3d(base + (0 + half) * kTileBytes, &tmap_q, &bars->load_full[b], h * kD, half * kTile, c);
-          tma_load_3d(base + (2 + half) * kTileBytes, &tmap_k, &bars->load_full[b], h * kD, half * kTile, c);
-          tma_load_3d(base + (4 + half) * kTileBytes, &tmap_v, &bars->load_full[b], h * kD, half * kTile, c);
-        }
-      };
-      constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
-      if (n_local > 0) load_item(0);
-      for (int n = 0; n < n_local; ++n) {
-        const int b = n & 1;
-        const uint32_t ph = static_cast<uint32_t>(n >> 1) & 1u;
-        uint8_t* base = smem + b * kItemBytes;
-        mbar_wait(&bars->load_full[b], ph, ctl, status, kErrWaitTma);
-        tc_fence_after_sync();
-        const uint64_t q0 = umma_desc_sw128(smem_u32(base)), q1 = umma_desc_sw128(smem_u32(base + kTileBytes));
-        const uint64_t k0 = umma_desc_sw128(smem_u32(base + 2 * kTileBytes));
-        const uint64_t k1 = umma_desc_sw128(smem_u32(base + 3 * kTileBytes));
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(tmem_base + 0, q0 + 2u * ks, k0 + 2u * ks, idesc_qk, ks != 0);
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(tmem_base + 128, q1 + 2u * ks, k0 + 2u * ks, idesc_qk, ks != 0);
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(tmem_base + 256, q1 + 2u * ks, k1 + 2u * ks, idesc_qk, ks != 0);
-        tc_commit(&bars->s_full);
-        if (n + 1 < n_local) {
-          // The other buffer was last read by the P V products of item n-1.
-          if (n >= 1) mbar_wait(&bars->buf_free[b ^ 1], static_cast<uint32_t>((n - 1) >> 1) & 1u, ctl, status, kErrWaitMma);
-          load_item(n + 1);
-        }
-        const uint64_t v0 = umma_desc_sw128(smem_u32(base + 4 * kTileBytes));
-        const uint64_t v1 = umma_desc_sw128(smem_u32(base + 5 * kTileBytes));
-        // rows 0-127: O0 = P00 V0 (P00 lives where Q0, Q1 were)
-        mbar_wait(&bars->p_full[0], static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitConsumer);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-          const uint64_t p = umma_desc_sw128(smem_u32(base + (ks >> 2) * kTileBytes)) + 2u * (ks & 3);
-          tc_mma_ss(tmem_base + 384, p, v0 + static_cast<uint64_t>(ks) * 128u, idesc_pv, ks != 0);
-        }
-        tc_commit(&bars->o_full[0]);
-        // rows 128-255: O1 = P10 V0 + P11 V1 (P10 where K0, K1 were; P11 in the extra tile)
-        mbar_wait(&bars->p_full[1], static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitConsumer);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-          const uint64_t p = umma_desc_sw128(smem_u32(base + (2 + (ks >> 2)) * kTileBytes)) + 2u * (ks & 3);
-          tc_mma_ss(tmem_base + 448, p, v0 + static_cast<uint64_t>(ks) * 128u, idesc_pv, ks != 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-          const uint64_t p = umma_desc_sw128(smem_u32(smem_p11 + (ks >> 2) * kTileBytes)) + 2u * (ks & 3);
-          tc_mma_ss(tmem_base + 448, p, v1 + static_cast<uint64_t>(ks) * 128u, idesc_pv, 1u);
-        }
-        tc_commit(&bars->o_full[1]);
-        tc_commit(&bars->buf_free[b]);
-      }
-    }
-  } else {
-    const int qt = warp >> 2;                 // which 128-frame half of the clip
-    const int lg = warp & 3;                  // TMEM lane group
-    const int r = lg * 32 + lane;             // row inside the half == TMEM lane
-    const int i = qt * kTile + r;             // query frame
-    const uint32_t lane_sel = static_cast<uint32_t>(lg * 32) << 16;
-    const int n_tiles = qt + 1;
-    for (int n = 0; n < n_local; ++n) {
-      const int item = blockIdx.x + n * gridDim.x;
-      const int c = item >> 3, h = item & 7, b = n & 1;
-      uint8_t* base = smem + b * kItemBytes;
-      mbar_wait(&bars->s_full, static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitMma);
-      tc_fence_after_sync();
-      // Pass 1: maximum over every visible score of the row (raw scores; the positive scale is applied
-      // once to the maximum).  A 32-column group is skipped when no row of the warp can see it and is
-      // masked element-wise only when some row of the warp cannot see all of it.
-      float m_raw = -INFINITY;
-#pragma unroll 1
-      for (int tile = 0; tile < n_tiles; ++tile) {
-        const int k0 = tile * kTile;
-        const uint32_t s_addr = tmem_base + lane_sel + (qt == 0 ? 0u : 128u + 128u * tile);
-        const int vis_lo = i - window + 1 - k0, vis_hi = i - k0;
-        const int w_row0 = qt * kTile + lg * 32;   // first frame of this warp
-        const int any_lo = w_row0 - window + 1 - k0, any_hi = w_row0 + 31 - k0;   // seen by at least one row
-        const int all_lo = w_row0 + 31 - window + 1 - k0, all_hi = w_row0 - k0;   // seen by every row
-#pragma unroll 1
-        for (int c0 = 0; c0 < kTile; c0 += 32) {
-          if (c0 > any_hi || c0 + 31 < any_lo) continue;
-          uint32_t s[32];
-          tmem_ld32(s_addr + c0, s);
-          tmem_ld_wait();
-          if (c0 >= all_lo && c0 + 31 <= all_hi) {
-#pragma unroll
-            for (int cc = 0; cc < 32; ++cc) m_raw = fmaxf(m_raw, __uint_as_float(s[cc]));
-          } else {
-#pragma unroll
-            for (int cc = 0; cc < 32; ++cc)
-              if (c0 + cc >= vis_lo && c0 + cc <= vis_hi) m_raw = fmaxf(m_raw, __uint_as_float(s[cc]));
-          }
-        }
-      }
-      const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
-      // Pass 2: probabilities -> swizzled 16-bit P tiles, row sum.
-      float l_row = 0.f;
-#pragma unroll 1
-      for (int tile = 0; tile < n_tiles; ++tile) {
-        const int k0 = tile * kTile;
-        const uint32_t s_addr = tmem_base + lane_sel + (qt == 0 ? 0u : 128u + 128u * tile);
-        uint8_t* p_tile = qt == 0 ? base : (tile == 0 ? base + 2 * kTileBytes : smem_p11);
-        const int vis_lo = i - window + 1 - k0, vis_hi = i - k0;
-        const int w_row0 = qt * kTile + lg * 32;
-        const int any_lo = w_row0 - window + 1 - k0, any_hi = w_row0 + 31 - k0;
-        const int all_lo = w_row0 + 31 - window + 1 - k0, all_hi = w_row0 - k0;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kTile; c0 += 32) {
-          uint8_t* half_base = p_tile + (c0 >> 6) * kTileBytes;
-          const int chunk0 = (c0 & 63) >> 3;
-          if (c0 > any_hi || c0 + 31 < any_lo) {
-#pragma unroll
-            for (int cc = 0; cc < 4; ++cc)
-              *reinterpret_cast<uint4*>(half_base + sw128_offset(r, chunk0 + cc)) = make_uint4(0u, 0u, 0u, 0u);
-            continue;
-          }
-          uint32_t s[32];
-          tmem_ld32(s_addr + c0, s);
-          tmem_ld_wait();
-          uint32_t pk[16];
-          if (c0 >= all_lo && c0 + 31 <= all_hi) {
-#pragma unroll
-            for (int cc = 0; cc < 32; cc += 2) {
-              const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc]), scale_log2e, -m_use));
-              const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc + 1]), scale_log2e, -m_use));
-              pk[cc / 2] = Pack16<VT>::pack(p0, p1);
-              l_row += p0 + p1;
-            }
-          } else {
-#pragma unroll
-            for (int cc = 0; cc < 32; cc += 2) {
-              float p[2];
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const bool vis = c0 + cc + e >= vis_lo && c0 + cc + e <= vis_hi;
-                p[e] = vis ? ex2_approx(fmaf(__uint_as_float(s[cc + e]), scale_log2e, -m_use)) : 0.f;
-              }
-              pk[cc / 2] = Pack16<VT>::pack(p[0], p[1]);
-              l_row += p[0] + p[1];
-            }
-          }
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc)
-            *reinterpret_cast<uint4*>(half_base + sw128_offset(r, chunk0 + cc)) =
-                make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
-        }
-      }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[qt]);
-
-      mbar_wait(&bars->o_full[qt], static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitMma);
-      tc_fence_after_sync();
-      const float inv = 1.f / l_row;
-      uint4* dst = reinterpret_cast<uint4*>(out + (static_cast<long long>(c) * T + i) * 512 + h * kD);
-#pragma unroll
-      for (int d0 = 0; d0 < kD; d0 += 32) {
-        uint32_t o[32];
-        tmem_ld32(tmem_base + lane_sel + 384 + qt * kD + d0, o);
-        tmem_ld_wait();
-        if (i < T) {
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              w[e] = Pack16<VT>::pack(__uint_as_float(o[8 * cc + 2 * e]) * inv, __uint_as_float(o[8 * cc + 2 * e + 1]) * inv);
-            dst[d0 / 8 + cc] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-      }
-      tc_fence_before_sync();
-    }
-  }
-
-  tc_fence_before_sync();
-  __syncthreads();
-  if (ctl->abort) __nanosleep(20000);
-  if (warp == 8) {
-    __syncwarp();
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
-  }
-}
-
-int launch_band_attn_clip(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* out, int B, int T,
-                          int window, float scale, int value_is_fp16, int* status, cudaStream_t st) {
-  using namespace clip;
-  auto kern = value_is_fp16 ? band_attn_clip_kernel<__half> : band_attn_clip_kernel<__nv_bfloat16>;
-  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
-  if (rc != 0) return rc;
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int n_items = B * 8;
-  const int grid = n_items < sms ? n_items : sms;
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, static_cast<uint16_t*>(out), n_items, T, window,
-                                          scale * 1.4426950408889634f, status);
   return static_cast<int>(cudaGetLastError());
 }
 
