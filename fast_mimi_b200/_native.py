@@ -20,6 +20,7 @@ SIGNATURES: dict[str, list] = {
     "fm_qkv_rope_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _P, _P],
     "fm_band_attn_prefill_bf16": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_prefill_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
+    "fm_attention_prefill_static_bf16": [_P, _P, _P, _P, _LL, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_decode_step_bf16": [_P, _P, _P, _P, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _F, _I, _P, _P],
     "fm_ring_attn_decode_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_band_attn_fp32_verify": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
@@ -61,5 +62,6 @@ def check(rc: int, what: str) -> None:
     (src/fast_mimi/_native_cutlass.py:163-164)."""
     if rc != 0:
         kind = {-1: "rejected geometry", -2: "grid too large", -3: "misaligned pointer",
-                -4: "cuTensorMapEncodeTiled unavailable"}.get(rc, "CUDA error" if rc > 0 else "error")
+                -4: "cuTensorMapEncodeTiled unavailable",
+                -5: "more frames than the built-in workspace holds"}.get(rc, "CUDA error" if rc > 0 else "error")
         raise RuntimeError(f"{what} failed with status {rc} ({kind})")

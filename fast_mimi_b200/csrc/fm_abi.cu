@@ -144,6 +144,50 @@ int fm_rope_fp32_verify(float* t, const float* cos, const float* sin, int B, int
   return fm::launch_rope_fp32(t, cos, sin, B, T, H, D, cos_bstride, static_cast<cudaStream_t>(stream));
 }
 
+// ---- entry point that allocates nothing -----------------------------------------------------------
+// Workspace for fm_attention_prefill_static_bf16: rotated q, k and v of up to FM_STATIC_MAX_FRAMES frames
+// (3 x 8192 x 512 x 2 B = 24 MiB).  It is part of the loaded module image, so every GPU that loads the
+// library holds it until the process exits.
+static __device__ __align__(256) unsigned short g_static_qkv[3ull * FM_STATIC_MAX_FRAMES * 512];
+
+// Device address of g_static_qkv on the current device.  In host code the array's name is only a handle
+// for the runtime, not something a kernel can dereference, so the address is asked for once per device.
+static int static_workspace(unsigned short** out) {
+  constexpr int kMaxDev = 64;
+  static std::mutex mu;
+  static unsigned short* ptrs[kMaxDev];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDev) return -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_qkv);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    ptrs[dev] = static_cast<unsigned short*>(p);
+  }
+  *out = ptrs[dev];
+  return 0;
+}
+
+int fm_attention_prefill_static_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
+                                     long long cos_bstride, void* out, int B, int T, int window, float scale,
+                                     int value_dtype, int* status, void* stream) {
+  if (B < 0 || T < 0) return -1;
+  const long long frames = static_cast<long long>(B) * T;
+  if (frames > FM_STATIC_MAX_FRAMES) return -5;     // larger than the built-in workspace
+  if (frames == 0) return 0;
+  unsigned short* ws = nullptr;
+  const int rc = static_workspace(&ws);
+  if (rc != 0) return rc;
+  unsigned short* q_ws = ws;
+  unsigned short* k_ws = ws + frames * 512;
+  unsigned short* v_ws = ws + 2 * frames * 512;
+  return fm_attention_prefill_bf16(x, w_qkv, cos, sin, cos_bstride, q_ws, k_ws, v_ws, out, B, T, window, scale,
+                                   value_dtype, status, stream);
+}
+
 int fm_read_status(const int* status, void* stream) {
   cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return static_cast<int>(e);

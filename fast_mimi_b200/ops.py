@@ -142,6 +142,35 @@ def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtyp
     return out
 
 
+STATIC_MAX_FRAMES = 8192
+
+
+def attention_prefill_static(x, w_qkv, cos, sin, out, *, window=250, scale=0.125, status=None):
+    """``attention_prefill`` for hosts that must not allocate device memory while it runs (an
+    allocation-free real-time audio callback, a plugin whose host application owns all device memory, a
+    process with a fixed device-memory budget):
+    the q/k/v workspace is a fixed 24 MiB array inside the library, so at most ``STATIC_MAX_FRAMES`` frames
+    (B*T <= 8192) per call, and ``out`` must be supplied by the caller.  Calls share that workspace: do not
+    let two of them overlap on the GPU.  Make the first call on a device outside any stream capture."""
+    lib = _native.load()
+    _need(x.dim() == 3, "x must be [B, T, 512]")
+    B, T, _ = x.shape
+    _check_frames(x, "x", torch.bfloat16)
+    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
+          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    bstride = _check_tables(cos, sin, B, T)
+    _need(out is not None and out.dtype in _VALUE_CODES, "out must be a float16 or bfloat16 tensor supplied by the caller")
+    _check_frames(out, "out", out.dtype, B * T)
+    if B * T > STATIC_MAX_FRAMES:
+        raise RuntimeError(f"{B * T} frames exceed the built-in workspace of {STATIC_MAX_FRAMES} frames; "
+                           "use attention_prefill with caller-provided workspaces")
+    rc = lib.fm_attention_prefill_static_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
+                                              out.data_ptr(), B, T, window, scale, _VALUE_CODES[out.dtype],
+                                              _status_ptr(status, x), _stream())
+    _native.check(rc, "fm_attention_prefill_static_bf16")
+    return out
+
+
 def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_workspace=None, out=None,
                 stream_pos=None, status=None):
     """One streaming step.  ``x [S,512] bf16``; ``ring_k/ring_v [S,8,slots,64]``; the new frame of

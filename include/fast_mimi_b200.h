@@ -52,6 +52,27 @@ int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos
                               long long cos_bstride, void* q_ws, void* k_ws, void* v_ws, void* out, int B,
                               int T, int window, float scale, int value_dtype, int* status, void* stream);
 
+/* Same computation as fm_attention_prefill_bf16 for callers that cannot hand over workspaces.
+ * (No counterpart in the reference, whose launchers always receive caller-allocated buffers.)
+ * Some hosts of this library may not call cudaMalloc at all: an allocation-free real-time audio loop
+ * (an allocation can stall for milliseconds and drop frames), plugins whose host application owns every
+ * device allocation, processes that budgeted their device memory up front.  For them the rotated q, k, v go to a
+ * workspace that is part of the library image: a file-scope __device__ array of
+ * FM_STATIC_MAX_FRAMES (8192) frames = 24 MiB, present on every GPU that loads the library until the
+ * process exits.  The call allocates nothing and frees nothing.
+ *   - B*T above FM_STATIC_MAX_FRAMES is rejected with -5 before anything is launched.
+ *   - The first call on each device looks the workspace address up (one host-side runtime query, no
+ *     launch); make that first call before starting any stream capture.
+ *   - All calls share the one workspace and it keeps the previous call's contents.  Nothing in it needs
+ *     to start at zero: the projection overwrites every frame row that the attention then reads.  Two
+ *     calls whose kernels can overlap on the GPU (different streams, or the same stream from different
+ *     threads without ordering) race on it; serialise them.
+ * x, w_qkv, cos, sin, out, status, stream: as fm_attention_prefill_bf16. */
+#define FM_STATIC_MAX_FRAMES 8192
+int fm_attention_prefill_static_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
+                                     long long cos_bstride, void* out, int B, int T, int window, float scale,
+                                     int value_dtype, int* status, void* stream);
+
 /* One streaming step for S streams: project the new frame, rotate q/k at the stream's position,
  * write k/v into slot (position % ring_slots) of the stream's ring, attend over the valid slots.
  * Replaces MimiKVCache.update + one-query SDPA (src/fast_mimi/model.py:1912-1914, 435-471, 1860-1868).
