@@ -56,3 +56,47 @@ def regen_attention_layer(seed: int, b: int, t: int, hidden: int = 512, std: flo
     wq, wk, wv, wo = regen_projections(seed, hidden, std)
     x = torch.randn(b, t, hidden).bfloat16().float()
     return x, wq, wk, wv, wo
+
+
+def fill_state_by_recipe(state: dict, seed: int = 0) -> dict:
+    """Deterministic weights for a full-size Mimi model, independent of module construction order: walk the
+    state dict in key order and draw every tensor from one seeded generator (codebook usage U[0.5,1.5),
+    codebook sums N(0,1), LayerNorm weights U[0.9,1.1), biases N(0,0.01^2), layer scales 0.01, matrices and
+    convolution kernels N(0, 1/fan_in)).  The reference's own fixture does the same with other constants
+    (tests/conftest.py:41-53 of the reference); a default-constructed model has all-zero codebooks."""
+    import math
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for name, v in state.items():
+            if name.endswith(".initialized"):
+                v.fill_(1)
+            elif name.endswith(".cluster_usage"):
+                v.copy_(torch.rand(v.shape, generator=g) + 0.5)
+            elif name.endswith(".embed_sum"):
+                v.copy_(torch.randn(v.shape, generator=g))
+            elif "layernorm.weight" in name:
+                v.copy_(torch.rand(v.shape, generator=g) * 0.2 + 0.9)
+            elif "layernorm.bias" in name or name.endswith(".bias"):
+                v.copy_(torch.randn(v.shape, generator=g) * 0.01)
+            elif name.endswith("layer_scale.scale"):
+                v.fill_(0.01)
+            elif v.dim() >= 2:
+                v.copy_(torch.randn(v.shape, generator=g) / math.sqrt(v[0].numel()))
+            else:
+                v.copy_(torch.randn(v.shape, generator=g) * 0.05)
+    return state
+
+
+def synthetic_audio(seed: int = 0, seconds: int = 5, rate: int = 24000) -> torch.Tensor:
+    """BASELINE config 1 input: harmonic series f0~U[90,250] Hz, 20 partials at 1/k amplitude, 4 Hz AM
+    envelope, N(0,0.01) noise, normalised to 0.1 RMS; shape [1, 1, seconds*rate]."""
+    import math
+    g = torch.Generator().manual_seed(seed)
+    n = seconds * rate
+    t = torch.arange(n, dtype=torch.float64) / rate
+    f0 = 90.0 + 160.0 * torch.rand(1, generator=g, dtype=torch.float64)
+    sig = sum(torch.sin(2 * math.pi * f0 * k * t) / k for k in range(1, 21))
+    sig = sig * (0.6 + 0.4 * torch.sin(2 * math.pi * 4.0 * t))
+    sig = sig + 0.01 * torch.randn(n, generator=g, dtype=torch.float64)
+    sig = sig * (0.1 / sig.pow(2).mean().sqrt())
+    return sig.float().view(1, 1, n)

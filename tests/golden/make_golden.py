@@ -181,47 +181,39 @@ def transformer_stack_tiny():
          **{"p." + k: v for k, v in state.items()})
 
 
-def synthetic_audio(seed=0, seconds=5, rate=24000):
-    """BASELINE config 1 input: harmonic series f0~U[90,250] Hz, 20 partials at 1/k amplitude,
-    4 Hz AM envelope, N(0,0.01) noise, normalised to 0.1 RMS."""
-    g = torch.Generator().manual_seed(seed)
-    n = seconds * rate
-    t = torch.arange(n, dtype=torch.float64) / rate
-    f0 = 90.0 + 160.0 * torch.rand(1, generator=g, dtype=torch.float64)
-    sig = sum(torch.sin(2 * math.pi * f0 * k * t) / k for k in range(1, 21))
-    sig = sig * (0.6 + 0.4 * torch.sin(2 * math.pi * 4.0 * t))
-    sig = sig + 0.01 * torch.randn(n, generator=g, dtype=torch.float64)
-    sig = sig * (0.1 / sig.pow(2).mean().sqrt())
-    return sig.float().view(1, 1, n)
-
-
 def end_to_end_codes():
-    """BASELINE config 1: full Mimi forward on CPU, random-init seed 0 with randomised codebook
-    buffers (a default-constructed model has all-zero codebooks -> every code would be 0)."""
+    """BASELINE config 1: full Mimi forward on CPU (5 s synthetic audio, 8 codebooks) with the weight recipe
+    of tests/conftest.py::fill_state_by_recipe, through the reference MimiModel and its functional runtime;
+    HF Transformers' MimiModel (the implementation the reference's own tests compare against) is loaded with
+    the same state and must give the same codes, which is what lets it stand in on the GPU box."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    from conftest import fill_state_by_recipe, synthetic_audio
     torch.manual_seed(0)
     model = MimiModel(MimiConfig(), attention_backend="sdpa").eval()
-    g = torch.Generator().manual_seed(0)
-    state = model.state_dict()
-    for name, value in state.items():
-        if name.endswith(".cluster_usage"):
-            value.copy_(torch.rand(value.shape, generator=g) + 0.5)
-        elif name.endswith(".embed_sum"):
-            value.copy_(torch.randn(value.shape, generator=g))
+    state = fill_state_by_recipe(model.state_dict(), seed=0)
     model.load_state_dict(state)
     audio = synthetic_audio()
     with torch.inference_mode():
-        enc = model.encode(audio, num_quantizers=8)
-        codes = enc.audio_codes
+        codes = model.encode(audio, num_quantizers=8).audio_codes
         functional = PureTorchMimi(model)
-        hidden = functional.encoder(audio)
-        enc_tr_in = hidden.transpose(1, 2)
+        enc_tr_in = functional.encoder(audio).transpose(1, 2)
         enc_tr_out = functional.transformer(enc_tr_in, "encoder_transformer")
+        f_codes = functional.quantizer_encode(functional.downsample(enc_tr_out.transpose(1, 2)), 8)
+    assert torch.equal(f_codes.reshape(codes.shape), codes), "functional runtime disagrees with the module path"
+    from transformers import MimiConfig as HFConfig, MimiModel as HFModel
+    hf_cfg = HFConfig(**MimiConfig().to_dict())
+    hf_cfg._attn_implementation = "sdpa"
+    hf = HFModel(hf_cfg).eval()
+    assert list(hf.state_dict()) == list(state)
+    hf.load_state_dict(state, strict=True)
+    with torch.inference_mode():
+        hf_codes = hf.encode(audio, num_quantizers=8).audio_codes
+    assert torch.equal(hf_codes, codes), "HF Transformers disagrees with the reference"
     probe = {k: state[k].flatten()[:4] for k in
              ("encoder_transformer.layers.0.self_attn.q_proj.weight",
               "decoder_transformer.layers.7.self_attn.o_proj.weight",
               "quantizer.semantic_residual_vector_quantizer.layers.0.codebook.embed_sum")}
-    save("e2e_codes_5s.npz", codes=codes, audio_probe=audio[0, 0, :16],
-         audio_rms=audio.pow(2).mean().sqrt(), enc_tr_in_probe=enc_tr_in[0, ::25, :8],
+    save("e2e_codes_5s.npz", codes=codes, audio_probe=audio[0, 0, :16], enc_tr_in_probe=enc_tr_in[0, ::25, :8],
          enc_tr_out_probe=enc_tr_out[0, ::25, :8], distinct_codes=len(torch.unique(codes)),
          **{"probe." + k: v for k, v in probe.items()})
     print("codes", tuple(codes.shape), "distinct", len(torch.unique(codes)))
