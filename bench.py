@@ -399,6 +399,88 @@ def profile_case(which: str) -> None:
     print(f"profile case {which}: done")
 
 
+def run_extra_workload(args) -> None:
+    """Secondary workloads of BASELINE.json, one JSON line each (single GPU; not the headline line):
+    longclip = config 4 (16 clips x 2500 frames, banded attention alone, rotated BF16 q,k / FP16 v resident);
+    stream   = config 5 (4096 streams x 500 one-frame steps x 8 layers from an empty 250-slot ring)."""
+    import fast_mimi_b200 as fm
+    from fast_mimi_b200 import ops
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    stream = torch.cuda.current_stream()
+    g = torch.Generator(device=dev).manual_seed(0)
+    if args.workload == "longclip":
+        B, T = 16, 2500
+        sets = []
+        for _ in range(3):      # three input sets in rotation: 492 MB, so no set survives in the 126 MB L2
+            q = (torch.randn(B, T, 512, device=dev, generator=g) / 8).bfloat16()
+            k = (torch.randn(B, T, 512, device=dev, generator=g) / 8).bfloat16()
+            v = (torch.randn(B, T, 512, device=dev, generator=g) / 8).half()
+            sets.append((q, k, v))
+        out = torch.empty_like(sets[0][2])
+        for i in range(max(args.warmup, 3)):
+            ops.band_attention_prefill(*sets[i % 3], window=WINDOW, out=out)
+        torch.cuda.synchronize()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(args.steps):
+            ops.band_attention_prefill(*sets[i % 3], window=WINDOW, out=out)
+        b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        flop = B * 2048 * pairs(T)
+        nbytes = 4 * B * T * 512 * 2
+        gbs = nbytes / (ms / 1e3) / 1e9
+        print(json.dumps({"metric": "attention frames/s", "value": B * T / (ms / 1e3), "unit": "frames/s", "n_gpus": 1,
+                          "steps": args.steps, "ms_per_step": ms, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "long-clip banded attention (BASELINE config 4), one layer call",
+                                     "clips": B, "frames": T, "window": WINDOW,
+                                     "l2": "three input sets in rotation (492 MB)"},
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                       "frac": gbs / peaks["hbm_gbs"], "kernel": "band_attn_prefill_kernel",
+                                       "tensor_tflops": flop / (ms / 1e3) / 1e12}}))
+        return
+    # stream: the whole of config 5
+    S, L, STEPS = 4096, 8, 500
+    ring = fm.MimiKVRing(L, S, WINDOW, device=dev)
+    ws = [(torch.randn(1536, HIDDEN, device=dev, generator=g) * 0.02).bfloat16() for _ in range(L)]
+    xs = [torch.randn(S, HIDDEN, device=dev, generator=g).bfloat16() for _ in range(4)]
+    pos = torch.arange(STEPS, device=dev, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, 2, device=dev, dtype=torch.int64).float() / 64))
+    emb = torch.cat((torch.outer(pos, inv),) * 2, -1)
+    cos, sin = emb.cos().contiguous(), emb.sin().contiguous()
+    qws = torch.empty_like(xs[0]); out = torch.empty(S, HIDDEN, device=dev, dtype=torch.float32)
+    status = ops.new_status(dev)
+
+    def run_all():
+        for t in range(STEPS):
+            c, s_ = cos[None, t:t + 1], sin[None, t:t + 1]
+            for l in range(L):
+                ops.decode_step(xs[(t + l) & 3], ws[l], c, s_, ring.ring_k[l], ring.ring_v[l], t, q_workspace=qws,
+                                out=out, status=status)
+
+    run_all()                      # warm-up pass (the ring is simply overwritten by the timed pass)
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    run_all()
+    b.record(stream)
+    torch.cuda.synchronize()
+    assert ops.read_status(status) == 0
+    ms = a.elapsed_time(b)
+    rows = sum(min(t + 1, WINDOW) for t in range(STEPS))
+    nbytes = S * L * (rows * 2 * 512 * 2 + STEPS * (2048 + 1024 + 2048)) + STEPS * L * 1536 * 512 * 2
+    gbs = nbytes / (ms / 1e3) / 1e9
+    print(json.dumps({"metric": "attention frames/s", "value": S * STEPS * L / (ms / 1e3), "unit": "frames/s", "n_gpus": 1,
+                      "steps": STEPS, "ms_total": ms, "ms_per_step": ms / STEPS, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "streaming decode (BASELINE config 5), 500 steps from an empty ring",
+                                 "streams": S, "layers": L, "ring_slots": WINDOW, "ring_gb": ring.bytes() / 1e9},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                   "frac": gbs / peaks["hbm_gbs"], "kernel": "qkv_rope_gemm_kernel + ring_decode_attn_kernel",
+                                   "algorithmic_bytes": nbytes}}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -408,9 +490,14 @@ def main() -> None:
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
     ap.add_argument("--profile-case", choices=["prefill", "decode"], help="run a small case for ncu and exit")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream"],
+                    help="prefill = headline (config 3); longclip / stream = configs 4 / 5, one extra JSON line")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)
+        return
+    if args.workload != "prefill":
+        run_extra_workload(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
