@@ -30,6 +30,7 @@ struct Ctl {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   CtaCtl ctl;
+  alignas(16) uint16_t qrow[kStages][64];   // the item's 64 query values, copied in with its ring slices
   float merge_m[kGroups][2][kWarps];
   float merge_l[kGroups][2][kWarps];
   float merge_o[kGroups][2][kWarps][64];
@@ -77,7 +78,8 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
         const uint32_t use = static_cast<uint32_t>(n / kStages);
         mbar_wait(&c->empty[st], (use & 1u) ^ 1u, ctl, status, kErrWaitConsumer);
         const uint32_t bytes = static_cast<uint32_t>(valid_slots(item)) * kRowBytes;
-        mbar_arrive_expect_tx(&c->full[st], 2 * bytes);
+        mbar_arrive_expect_tx(&c->full[st], 2 * bytes + 128);
+        bulk_load_1d(&c->qrow[st][0], q + static_cast<size_t>(item) * 64, 128, &c->full[st]);
         const size_t src = static_cast<size_t>(item) * ring_slots * 64;
         bulk_load_1d(stage_base + (2 * st) * tile_bytes, ring_k + src, bytes, &c->full[st]);
         bulk_load_1d(stage_base + (2 * st + 1) * tile_bytes, ring_v + src, bytes, &c->full[st]);
@@ -96,9 +98,12 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
       const uint32_t use = static_cast<uint32_t>(n / kStages);
       const int nv = valid_slots(static_cast<int>(item));
       const int s = static_cast<int>(item >> 3), h = static_cast<int>(item & 7);
+      mbar_wait(&c->full[st], use & 1u, ctl, status, kErrWaitTma);
+      const uint8_t* ks = stage_base + (2 * st) * tile_bytes;
+      const uint8_t* vs = stage_base + (2 * st + 1) * tile_bytes;
       float qf[8];
       {
-        const uint4 raw = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(s) * 512 + h * 64 + chunk * 8);
+        const uint4 raw = *reinterpret_cast<const uint4*>(&c->qrow[st][chunk * 8]);
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -107,9 +112,6 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
           qf[2 * e + 1] = f.y * scale_log2e;
         }
       }
-      mbar_wait(&c->full[st], use & 1u, ctl, status, kErrWaitTma);
-      const uint8_t* ks = stage_base + (2 * st) * tile_bytes;
-      const uint8_t* vs = stage_base + (2 * st + 1) * tile_bytes;
 
       float sc[16];
       float m_w = -INFINITY;

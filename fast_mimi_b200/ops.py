@@ -207,6 +207,45 @@ def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_
     return out
 
 
+class DecodePlan:
+    """A validated, pre-bound ``decode_step`` for a fixed set of buffers: geometry is checked once, and each
+    ``step`` is a single native call (the per-call checks of ``decode_step`` cost more host time than the
+    kernels of a nearly empty ring take).  Buffers must stay alive and unchanged in place."""
+
+    def __init__(self, x, w_qkv, ring_k, ring_v, *, scale=0.125, q_workspace=None, out=None, status=None):
+        self._lib = _native.load()
+        S = x.shape[0]
+        cos = torch.zeros(1, 1, HEAD_DIM, device=x.device)
+        # run the full validation once through the checked entry point's helpers
+        _need(x.dim() == 2, "x must be [S, 512]")
+        _check_frames(x, "x", torch.bfloat16)
+        _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
+              and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+        _check_tables(cos, cos, S, 1)
+        _need(ring_k.dim() == 4 and ring_k.shape[0] == S and ring_k.shape[1] == HEADS and ring_k.shape[3] == HEAD_DIM
+              and ring_k.is_cuda and ring_k.dtype == torch.bfloat16 and ring_k.is_contiguous(),
+              "ring_k must be contiguous bf16 [S, 8, slots, 64]")
+        _need(ring_v.is_cuda and ring_v.dtype in _VALUE_CODES and ring_v.is_contiguous() and ring_v.shape == ring_k.shape,
+              "ring_v must match ring_k (float16 or bfloat16)")
+        self.q_workspace = torch.empty_like(x) if q_workspace is None else q_workspace
+        _check_frames(self.q_workspace, "q workspace", torch.bfloat16, S)
+        self.out = torch.empty((S, HIDDEN), dtype=torch.float32, device=x.device) if out is None else out
+        _need(self.out.is_cuda and self.out.dtype == torch.float32 and self.out.is_contiguous()
+              and self.out.numel() == S * HIDDEN, "out must be contiguous float32 [S, 512]")
+        self._keep = (x, w_qkv, ring_k, ring_v, status)
+        self._args_head = (x.data_ptr(), w_qkv.data_ptr())
+        self._args_tail = (self.q_workspace.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), self.out.data_ptr(), S,
+                           ring_k.shape[2], float(scale), _VALUE_CODES[ring_v.dtype], _status_ptr(status, x))
+
+    def step(self, position: int, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """``cos, sin``: contiguous float32 ``[1, 1, 64]`` tables of the new frame's position."""
+        rc = self._lib.fm_decode_step_bf16(*self._args_head, cos.data_ptr(), sin.data_ptr(), 0, None, int(position),
+                                           *self._args_tail, _stream())
+        if rc != 0:
+            _native.check(rc, "fm_decode_step_bf16")
+        return self.out
+
+
 def _strides3(t: torch.Tensor, frame_major: bool) -> list[int]:
     # (batch, head, time) strides in elements for a 4-D tensor whose last dim is contiguous.
     if frame_major:     # [B, T, H, D]
