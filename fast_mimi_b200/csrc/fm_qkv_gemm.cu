@@ -10,8 +10,10 @@
 // 128-frame tile of x, loaded once by TMA and kept in shared memory (128 KB), and loads HALF of every
 // 256x64 W_qkv tile (128 weight rows); one tcgen05.mma issued by the pair's leader multiplies the
 // 256 frames of both CTAs by all 256 weight rows, so each W byte is fetched from L2 once per 256 frames.
-// Each CTA's 128x256 FP32 result lands in its own TMEM (two 256-column buffers: the epilogue of output
-// tile n overlaps the MMAs of tile n+1).  Epilogue warps read one frame row per thread (both halves of
+// Each CTA's 128x256 FP32 result lands in its own TMEM (two 256-column buffers: the epilogue of one work
+// unit overlaps the MMAs of the next).  The kernel is persistent: 74 pairs walk contiguous ranges of
+// (frame-tile pair, output tile) units, and while the last output tile of a frame tile is being multiplied
+// the x chunks it has finished with are already replaced by the next frame tile's.  Epilogue warps read one frame row per thread (both halves of
 // a RoPE pair sit in the same row), rotate, round, stage 32x64 slabs in swizzled shared memory and write
 // them with TMA stores (full 128-byte lines).  Warps 0-7: epilogue (two per TMEM lane group, two heads
 // each).  Warp 8: TMA producer (+ TMEM allocation).  Warp 9: MMA issuer (leader CTA only).
@@ -38,6 +40,7 @@ constexpr int kSmemBytes = 1024 /*align*/ + kKChunks * kABytes + kStages * kBByt
 
 struct Barriers {
   uint64_t a_full[kKChunks];   // used in the leader: bytes of both CTAs' x chunks
+  uint64_t a_empty[kKChunks];  // per CTA: the chunk's last MMA of the current frame tile has completed
   uint64_t b_full[kStages];    // used in the leader: bytes of both halves of a W tile
   uint64_t b_empty[kStages];   // per CTA: stage consumed by the tensor core
   uint64_t acc_full[2];        // per CTA: accumulator buffer complete
@@ -53,7 +56,7 @@ template <typename VT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm::kThreads, 1)
 qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                     const __grid_constant__ CUtensorMap tmap_v, QkvEpilogueArgs ep, int M, int n_tiles_per_cta,
+                     const __grid_constant__ CUtensorMap tmap_v, QkvEpilogueArgs ep, int M, int total_units,
                      int* status) {
   using namespace gemm;
   extern __shared__ uint8_t smem_raw[];
@@ -67,11 +70,19 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();      // 0 = pair leader
   const bool leader = rank == 0;
-  const int m0 = blockIdx.x * kBlockM;
-  const int n_first = blockIdx.y * n_tiles_per_cta;
+  // Work units = (pair of 128-frame tiles, 256-wide output tile), numbered frame-tile-major, so that a
+  // pair walks the six output tiles of one frame tile before moving to the next.  Each pair takes a
+  // contiguous range of units.
+  const int pair = static_cast<int>(blockIdx.x >> 1), n_pairs = static_cast<int>(gridDim.x >> 1);
+  const int u_base = total_units / n_pairs, u_extra = total_units % n_pairs;
+  const int u_begin = pair * u_base + (pair < u_extra ? pair : u_extra);
+  const int u_count = u_base + (pair < u_extra ? 1 : 0);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kKChunks; ++i) mbar_init(&bars->a_full[i], 1);
+    for (int i = 0; i < kKChunks; ++i) {
+      mbar_init(&bars->a_full[i], 1);
+      mbar_init(&bars->a_empty[i], 1);
+    }
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&bars->b_full[i], 1);
       mbar_init(&bars->b_empty[i], 1);
@@ -104,19 +115,37 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
       tma_prefetch_desc(&tmap_w);
-      for (int kc = 0; kc < kKChunks; ++kc) {
+      auto load_a = [&](int kc, int frame_tile, int gen) {
+        // The chunk's buffer is reused: its MMAs of the previous frame tile must have completed.
+        if (gen > 0) mbar_wait(&bars->a_empty[kc], static_cast<uint32_t>(gen - 1) & 1u, ctl, status, kErrWaitMma);
         if (leader) mbar_arrive_expect_tx(&bars->a_full[kc], 2 * kABytes);
-        tma_load_2d_pair(smem_a + kc * kABytes, &tmap_x, &bars->a_full[kc], kc * kBlockK, m0);
-      }
-      int stage = 0;
+        tma_load_2d_pair(smem_a + kc * kABytes, &tmap_x, &bars->a_full[kc], kc * kBlockK,
+                         (2 * frame_tile + static_cast<int>(rank)) * kBlockM);
+      };
+      int stage = 0, gen = -1, cur_tile = -1, preloaded = 0;
       uint32_t phase = 0;
-      for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
-        const int n0 = (n_first + nt) * kBlockN + static_cast<int>(rank) * kHalfN;
+      for (int i = 0; i < u_count; ++i) {
+        const int u = u_begin + i, frame_tile = u / 6, ntile = u % 6;
+        if (frame_tile != cur_tile) {
+          ++gen;
+          cur_tile = frame_tile;
+          for (int kc = preloaded; kc < kKChunks; ++kc) load_a(kc, frame_tile, gen);
+          preloaded = 0;
+        }
+        const int next_tile = (i + 1 < u_count) ? (u + 1) / 6 : -1;
+        const bool roll = next_tile >= 0 && next_tile != frame_tile;   // last unit of this frame tile
+        const int n0 = ntile * kBlockN + static_cast<int>(rank) * kHalfN;
         for (int kc = 0; kc < kKChunks; ++kc) {
           mbar_wait(&bars->b_empty[stage], phase ^ 1u, ctl, status, kErrWaitConsumer);
           if (leader) mbar_arrive_expect_tx(&bars->b_full[stage], 2 * kBBytes);
           tma_load_2d_pair(smem_b + stage * kBBytes, &tmap_w, &bars->b_full[stage], kc * kBlockK, n0);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          // W stage kc reuses the buffer of stage kc-4, so chunk kc-4's MMAs of this unit are done and
+          // the x chunk can already be replaced by the next frame tile's.
+          if (roll && kc >= kStages) {
+            load_a(kc - kStages, next_tile, gen + 1);
+            preloaded = kc - kStages + 1;
+          }
         }
       }
     }
@@ -124,16 +153,21 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, 1, 1, 0, 0);
-      int stage = 0;
+      int stage = 0, gen = -1, cur_tile = -1;
       uint32_t phase = 0;
-      for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
-        const int buf = nt & 1;
-        const uint32_t use = static_cast<uint32_t>(nt >> 1);
+      for (int i = 0; i < u_count; ++i) {
+        const int u = u_begin + i, frame_tile = u / 6;
+        const bool fresh = frame_tile != cur_tile;        // first unit of a frame tile: wait for its x chunks
+        if (fresh) { ++gen; cur_tile = frame_tile; }
+        const int next_tile = (i + 1 < u_count) ? (u + 1) / 6 : -1;
+        const bool roll = next_tile >= 0 && next_tile != frame_tile;
+        const int buf = i & 1;
+        const uint32_t use = static_cast<uint32_t>(i >> 1);
         mbar_wait(&bars->acc_empty[buf], (use & 1u) ^ 1u, ctl, status, kErrWaitConsumer);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBlockN);
         for (int kc = 0; kc < kKChunks; ++kc) {
-          if (nt == 0) mbar_wait(&bars->a_full[kc], 0, ctl, status, kErrWaitTma);
+          if (fresh) mbar_wait(&bars->a_full[kc], static_cast<uint32_t>(gen) & 1u, ctl, status, kErrWaitTma);
           mbar_wait(&bars->b_full[stage], phase, ctl, status, kErrWaitTma);
           tc_fence_after_sync();
           const uint64_t a_desc = umma_desc_sw128(smem_u32(smem_a + kc * kABytes));
@@ -144,6 +178,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
             tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
           }
           tc_commit_pair(&bars->b_empty[stage], 3);     // frees the stage in both CTAs
+          if (roll) tc_commit_pair(&bars->a_empty[kc], 3);   // and, on a tile's last unit, the x chunk
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         tc_commit_pair(&bars->acc_full[buf], 3);        // both CTAs' epilogues may read their TMEM
@@ -154,38 +189,46 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     const int lg = warp & 3;      // TMEM lane group: frames 32*lg .. 32*lg+31 of the tile
     const int hsel = warp >> 2;   // which two of the tile's four heads this warp handles
     const int row_in_tile = lg * 32 + lane;
-    const long long row = static_cast<long long>(m0) + row_in_tile;
-    const bool row_ok = row < M;
-    const int clip = row_ok ? static_cast<int>(row / ep.T) : 0;
-    const int t = row_ok ? static_cast<int>(row % ep.T) : 0;
-    // RoPE factors of this thread's frame, kept in registers for all heads of q and k.  The table's two
-    // 32-wide halves are identical by construction (frequencies repeated), so only the first is read.
-    float rc[32], rs[32];
-    if (n_first < 4 && row_ok) {
-      const float4* c4 = reinterpret_cast<const float4*>(ep.cos + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
-      const float4* s4 = reinterpret_cast<const float4*>(ep.sin + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 c = __ldg(c4 + i), sn = __ldg(s4 + i);
-        rc[4 * i] = c.x; rc[4 * i + 1] = c.y; rc[4 * i + 2] = c.z; rc[4 * i + 3] = c.w;
-        rs[4 * i] = sn.x; rs[4 * i + 1] = sn.y; rs[4 * i + 2] = sn.z; rs[4 * i + 3] = sn.w;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) { rc[i] = 1.f; rs[i] = 0.f; }
-    }
-    long long ring_row = -1;
-    if (ep.ring_k != nullptr && row_ok) {
-      const int pos = ep.pos_base + (ep.clip_pos != nullptr ? ep.clip_pos[clip] : 0) + t;
-      // Only the newest ring_slots frames of a clip land in the ring.
-      if (t >= ep.T - ep.ring_slots) ring_row = static_cast<long long>(clip) * 8 * ep.ring_slots + pos % ep.ring_slots;
-    }
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(&bars->acc_empty[0]), 0);
     uint8_t* slab = smem_out + warp * kSlabBytes;
-    for (int nt = 0; nt < n_tiles_per_cta; ++nt) {
-      const int buf = nt & 1;
-      const uint32_t use = static_cast<uint32_t>(nt >> 1);
-      const int ntile = n_first + nt;
+    // Per frame tile: this thread's frame, its RoPE factors (kept in registers for all heads of q and k;
+    // the table's two 32-wide halves are identical by construction, so only the first is read) and its
+    // ring slot.
+    float rc[32], rs[32];
+    long long row = 0, ring_row = -1;
+    bool row_ok = false;
+    int m0 = 0, cur_tile = -1;
+    for (int i = 0; i < u_count; ++i) {
+      const int u = u_begin + i, frame_tile = u / 6, ntile = u % 6;
+      if (frame_tile != cur_tile) {
+        cur_tile = frame_tile;
+        m0 = (2 * frame_tile + static_cast<int>(rank)) * kBlockM;
+        row = static_cast<long long>(m0) + row_in_tile;
+        row_ok = row < M;
+        const int clip = row_ok ? static_cast<int>(row / ep.T) : 0;
+        const int t = row_ok ? static_cast<int>(row % ep.T) : 0;
+        if (row_ok) {
+          const float4* c4 = reinterpret_cast<const float4*>(ep.cos + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
+          const float4* s4 = reinterpret_cast<const float4*>(ep.sin + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 c = __ldg(c4 + j), sn = __ldg(s4 + j);
+            rc[4 * j] = c.x; rc[4 * j + 1] = c.y; rc[4 * j + 2] = c.z; rc[4 * j + 3] = c.w;
+            rs[4 * j] = sn.x; rs[4 * j + 1] = sn.y; rs[4 * j + 2] = sn.z; rs[4 * j + 3] = sn.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { rc[j] = 1.f; rs[j] = 0.f; }
+        }
+        ring_row = -1;
+        if (ep.ring_k != nullptr && row_ok) {
+          const int pos = ep.pos_base + (ep.clip_pos != nullptr ? ep.clip_pos[clip] : 0) + t;
+          // Only the newest ring_slots frames of a clip land in the ring.
+          if (t >= ep.T - ep.ring_slots) ring_row = static_cast<long long>(clip) * 8 * ep.ring_slots + pos % ep.ring_slots;
+        }
+      }
+      const int buf = i & 1;
+      const uint32_t use = static_cast<uint32_t>(i >> 1);
       const int seg = ntile >> 1;              // 0 = q, 1 = k, 2 = v
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
@@ -308,15 +351,17 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
   rc = encode_2d_16bit(&tmap_v, ep.v != nullptr ? ep.v : x, static_cast<uint64_t>(M), 512, 32, 64);
   if (rc != 0) return rc;
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
-  const int m_ctas = (m_tiles + 1) & ~1;   // CTAs come in pairs; an odd last tile gets an idle partner
-  // Few frame tiles (streaming decode): split the six 256-wide output tiles over CTA pairs too.
-  const int n_split = m_ctas >= 148 ? 1 : (m_ctas >= 50 ? 3 : 6);
-  const int per_cta = 6 / n_split;
-  dim3 grid(m_ctas, n_split);
+  const int pair_tiles = (m_tiles + 1) / 2;          // an odd last tile gets a partner that works on padding
+  const int total_units = pair_tiles * 6;            // (pair of frame tiles, 256-wide output tile)
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;   // persistent: one CTA per SM, CTAs in pairs
+  const int n_pairs = total_units < max_pairs ? total_units : max_pairs;
   auto kern = value_is_fp16 ? qkv_rope_gemm_kernel<__half> : qkv_rope_gemm_kernel<__nv_bfloat16>;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (rc != 0) return rc;
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, tmap_q, tmap_k, tmap_v, ep, M, per_cta, status);
+  kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, tmap_q, tmap_k, tmap_v, ep, M, total_units, status);
   return static_cast<int>(cudaGetLastError());
 }
 
