@@ -52,7 +52,8 @@ def window_attention_fp32(query, key, value, *, scale, window, q_offset=0, k_off
 
 class MimiAttentionB200(nn.Module):
     def __init__(self, hidden_size: int = 512, num_heads: int = 8, head_dim: int = 64, sliding_window: int = 250,
-                 layer_idx: int = 0, precision: str = "tc", value_dtype: torch.dtype = torch.float16) -> None:
+                 layer_idx: int = 0, precision: str = "tc", value_dtype: torch.dtype = torch.float16,
+                 input_dtype: torch.dtype | None = None) -> None:
         super().__init__()
         if precision not in ("tc", "fp32"):
             raise ValueError("precision must be 'tc' or 'fp32'")
@@ -66,6 +67,10 @@ class MimiAttentionB200(nn.Module):
         self.sliding_window = sliding_window
         self.precision = precision
         self.value_dtype = value_dtype
+        # Type in which activations and the packed projection weight reach the tensor core.  None = FP16
+        # for FP32 / FP16 callers (8x finer rounding than BF16 at the same rate; LayerNorm-ed activations
+        # and weights are far inside its range) and BF16 for BF16 callers.
+        self.input_dtype = input_dtype
         self.q_proj = nn.Linear(hidden_size, num_heads * head_dim, bias=False)
         self.k_proj = nn.Linear(hidden_size, num_heads * head_dim, bias=False)
         self.v_proj = nn.Linear(hidden_size, num_heads * head_dim, bias=False)
@@ -93,15 +98,20 @@ class MimiAttentionB200(nn.Module):
                               value_dtype=self.value_dtype)
         return LinearKVCache(num_layers, self.sliding_window)
 
-    def packed_qkv_weight(self) -> torch.Tensor:
-        """``cat(Wq, Wk, Wv)`` as BF16 ``[1536, 512]``, rebuilt when a projection weight changes (the
-        reference packs once the same way: src/fast_mimi/_packed_qkv.py:139-150)."""
+    def packed_qkv_weight(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """``cat(Wq, Wk, Wv)`` as a 16-bit ``[1536, 512]`` tensor, rebuilt when a projection weight changes
+        (the reference packs once the same way: src/fast_mimi/_packed_qkv.py:139-150)."""
         ws = (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
-        key = tuple((w.data_ptr(), w._version, w.device) for w in ws)
+        key = tuple((w.data_ptr(), w._version, w.device) for w in ws) + (dtype,)
         if self._packed is None or self._packed_key != key:
-            self._packed = torch.cat([w.detach() for w in ws], dim=0).to(torch.bfloat16).contiguous()
+            self._packed = torch.cat([w.detach() for w in ws], dim=0).to(dtype).contiguous()
             self._packed_key = key
         return self._packed
+
+    def _tc_input_dtype(self, hidden_states: torch.Tensor) -> torch.dtype:
+        if self.input_dtype is not None:
+            return self.input_dtype
+        return torch.bfloat16 if hidden_states.dtype == torch.bfloat16 else torch.float16
 
     # -------------------------------------------------------------------------------------------
     def forward(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor | None, past_key_values,
@@ -124,10 +134,11 @@ class MimiAttentionB200(nn.Module):
 
     def _forward_tc(self, hidden_states, cache, cos, sin):
         B, T, _ = hidden_states.shape
-        x = hidden_states.to(torch.bfloat16).contiguous()
+        in_dtype = self._tc_input_dtype(hidden_states)
+        x = hidden_states.to(in_dtype).contiguous()
         cos = cos.to(torch.float32).contiguous()
         sin = sin.to(torch.float32).contiguous()
-        w = self.packed_qkv_weight()
+        w = self.packed_qkv_weight(in_dtype)
         if cache is None:
             return ops.attention_prefill(x, w, cos, sin, window=self.sliding_window, scale=self.scaling,
                                          value_dtype=self.value_dtype)

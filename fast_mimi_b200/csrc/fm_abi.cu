@@ -68,7 +68,7 @@ int fm_abi_version(void) { return 1; }
 
 int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                      void* q, void* k, void* v, int B, int T, int value_dtype, int* status, void* stream) {
-  if (B < 0 || T < 0 || (value_dtype != 0 && value_dtype != 1)) return -1;
+  if (B < 0 || T < 0 || value_dtype < 0 || value_dtype > 3) return -1;
   if (static_cast<long long>(B) * T > 0x7fffffffLL) return -1;
   QkvEpilogueArgs ep = {};
   ep.q = static_cast<uint16_t*>(q);
@@ -94,7 +94,7 @@ int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos
                               int window, float scale, int value_dtype, int* status, void* stream) {
   int rc = fm_qkv_rope_bf16(x, w_qkv, cos, sin, cos_bstride, q_ws, k_ws, v_ws, B, T, value_dtype, status, stream);
   if (rc != 0) return rc;
-  return fm_band_attn_prefill_bf16(q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype, status, stream);
+  return fm_band_attn_prefill_bf16(q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype & 1, status, stream);
 }
 
 int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring_v, float* out,
@@ -108,7 +108,7 @@ int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring
 int fm_decode_step_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                         const int* stream_pos, int pos_base, void* q_ws, void* ring_k, void* ring_v, float* out,
                         int S, int ring_slots, float scale, int value_dtype, int* status, void* stream) {
-  if (S < 0 || (value_dtype != 0 && value_dtype != 1) || ring_slots <= 0 || ring_slots > 256) return -1;
+  if (S < 0 || value_dtype < 0 || value_dtype > 3 || ring_slots <= 0 || ring_slots > 256) return -1;
   if (ring_k == nullptr || ring_v == nullptr || q_ws == nullptr) return -1;
   QkvEpilogueArgs ep = {};
   ep.q = static_cast<uint16_t*>(q_ws);
@@ -124,7 +124,7 @@ int fm_decode_step_bf16(const void* x, const void* w_qkv, const float* cos, cons
   int rc = fm::launch_qkv_rope_gemm(x, w_qkv, ep, S, value_dtype, status, static_cast<cudaStream_t>(stream));
   if (rc != 0) return rc;
   return fm::launch_ring_decode_attn(q_ws, ring_k, ring_v, out, stream_pos, pos_base, S, ring_slots, scale,
-                                     value_dtype, status, static_cast<cudaStream_t>(stream));
+                                     value_dtype & 1, status, static_cast<cudaStream_t>(stream));
 }
 
 int fm_band_attn_fp32_verify(const float* q, const float* k, const float* v, float* out, int B, int H, int D, int Tq,

@@ -38,7 +38,7 @@ int launch_rope_fp32(float* t, const float* cosv, const float* sinv, int B, int 
 int launch_band_attn_fp32(const float* q, const float* k, const float* v, float* out, int B, int H, int D,
                           int Tq, int Tk, int q_off, int k_off, int window, float scale,
                           const long long* strides, cudaStream_t st);
-int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int value_is_fp16,
+int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int dtype_flags,
                          int* status, cudaStream_t st);
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st);

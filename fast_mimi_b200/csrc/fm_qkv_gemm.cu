@@ -57,7 +57,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm::kThreads, 1)
 qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, QkvEpilogueArgs ep, int M, int total_units,
-                     int* status) {
+                     uint32_t idesc, int* status) {
   using namespace gemm;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -152,7 +152,6 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   } else if (warp == kEpiWarps + 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, 1, 1, 0, 0);
       int stage = 0, gen = -1, cur_tile = -1;
       uint32_t phase = 0;
       for (int i = 0; i < u_count; ++i) {
@@ -328,7 +327,7 @@ static int encode_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, ui
                       CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int value_is_fp16,
+int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int dtype_flags,
                          int* status, cudaStream_t st) {
   using namespace gemm;
   if (M <= 0) return M == 0 ? 0 : -1;
@@ -358,10 +357,14 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;   // persistent: one CTA per SM, CTAs in pairs
   const int n_pairs = total_units < max_pairs ? total_units : max_pairs;
-  auto kern = value_is_fp16 ? qkv_rope_gemm_kernel<__half> : qkv_rope_gemm_kernel<__nv_bfloat16>;
+  // dtype_flags bit 0: v is written as FP16 (else BF16); bit 1: x and w_qkv hold FP16 (else BF16).
+  const int in_fmt = (dtype_flags & 2) ? 0 : 1;   // tcgen05 kind::f16 operand format: 0 = F16, 1 = BF16
+  const uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, in_fmt, in_fmt, 0, 0);
+  auto kern = (dtype_flags & 1) ? qkv_rope_gemm_kernel<__half> : qkv_rope_gemm_kernel<__nv_bfloat16>;
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (rc != 0) return rc;
-  kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, tmap_q, tmap_k, tmap_v, ep, M, total_units, status);
+  kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, tmap_q, tmap_k, tmap_v, ep, M, total_units, idesc,
+                                                      status);
   return static_cast<int>(cudaGetLastError());
 }
 

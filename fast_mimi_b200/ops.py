@@ -36,6 +36,18 @@ def _check_frames(t: torch.Tensor, name: str, dtype: torch.dtype, rows: int | No
         _need(t.numel() == rows * HIDDEN, f"{name} must hold {rows} frames")
 
 
+_INPUT_DTYPES = (torch.bfloat16, torch.float16)
+
+
+def _check_projection_inputs(x: torch.Tensor, w_qkv: torch.Tensor) -> int:
+    """x and the packed weight must share one 16-bit float type; returns the dtype-flag bit for FP16."""
+    _need(x.dtype in _INPUT_DTYPES, f"x must be bfloat16 or float16, got {x.dtype}")
+    _check_frames(x, "x", x.dtype)
+    _need(w_qkv.is_cuda and w_qkv.dtype == x.dtype and w_qkv.is_contiguous()
+          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), f"w_qkv must be contiguous {x.dtype} [1536, 512]")
+    return 2 if x.dtype == torch.float16 else 0
+
+
 def _check_tables(cos: torch.Tensor, sin: torch.Tensor, B: int, T: int) -> int:
     for name, t in (("cos", cos), ("sin", sin)):
         _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous(), f"{name} must be contiguous CUDA float32")
@@ -80,18 +92,18 @@ def qkv_rope(x, w_qkv, cos, sin, *, value_dtype=torch.float16, out=None, status=
     lib = _native.load()
     _need(x.dim() == 3, "x must be [B, T, 512]")
     B, T, _ = x.shape
-    _check_frames(x, "x", torch.bfloat16)
-    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
-          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    in_flag = _check_projection_inputs(x, w_qkv)
     bstride = _check_tables(cos, sin, B, T)
     if out is None:
-        out = (torch.empty_like(x), torch.empty_like(x), torch.empty(x.shape, dtype=value_dtype, device=x.device))
+        out = (torch.empty(x.shape, dtype=torch.bfloat16, device=x.device),
+               torch.empty(x.shape, dtype=torch.bfloat16, device=x.device),
+               torch.empty(x.shape, dtype=value_dtype, device=x.device))
     q, k, v = out
     _check_frames(q, "q", torch.bfloat16, B * T)
     _check_frames(k, "k", torch.bfloat16, B * T)
     _check_frames(v, "v", value_dtype, B * T)
     rc = lib.fm_qkv_rope_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
-                              q.data_ptr(), k.data_ptr(), v.data_ptr(), B, T, _VALUE_CODES[value_dtype],
+                              q.data_ptr(), k.data_ptr(), v.data_ptr(), B, T, _VALUE_CODES[value_dtype] | in_flag,
                               _status_ptr(status, x), _stream())
     _native.check(rc, "fm_qkv_rope_bf16")
     return q, k, v
@@ -121,12 +133,11 @@ def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtyp
     lib = _native.load()
     _need(x.dim() == 3, "x must be [B, T, 512]")
     B, T, _ = x.shape
-    _check_frames(x, "x", torch.bfloat16)
-    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
-          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    in_flag = _check_projection_inputs(x, w_qkv)
     bstride = _check_tables(cos, sin, B, T)
     if workspace is None:
-        workspace = (torch.empty_like(x), torch.empty_like(x),
+        workspace = (torch.empty(x.shape, dtype=torch.bfloat16, device=x.device),
+                     torch.empty(x.shape, dtype=torch.bfloat16, device=x.device),
                      torch.empty(x.shape, dtype=value_dtype, device=x.device))
     q, k, v = workspace
     _check_frames(q, "q workspace", torch.bfloat16, B * T)
@@ -137,7 +148,7 @@ def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtyp
     _check_frames(out, "out", value_dtype, B * T)
     rc = lib.fm_attention_prefill_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
                                        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, T, window,
-                                       scale, _VALUE_CODES[value_dtype], _status_ptr(status, x), _stream())
+                                       scale, _VALUE_CODES[value_dtype] | in_flag, _status_ptr(status, x), _stream())
     _native.check(rc, "fm_attention_prefill_bf16")
     return out
 
@@ -155,9 +166,7 @@ def attention_prefill_static(x, w_qkv, cos, sin, out, *, window=250, scale=0.125
     lib = _native.load()
     _need(x.dim() == 3, "x must be [B, T, 512]")
     B, T, _ = x.shape
-    _check_frames(x, "x", torch.bfloat16)
-    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
-          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    in_flag = _check_projection_inputs(x, w_qkv)
     bstride = _check_tables(cos, sin, B, T)
     _need(out is not None and out.dtype in _VALUE_CODES, "out must be a float16 or bfloat16 tensor supplied by the caller")
     _check_frames(out, "out", out.dtype, B * T)
@@ -165,7 +174,7 @@ def attention_prefill_static(x, w_qkv, cos, sin, out, *, window=250, scale=0.125
         raise RuntimeError(f"{B * T} frames exceed the built-in workspace of {STATIC_MAX_FRAMES} frames; "
                            "use attention_prefill with caller-provided workspaces")
     rc = lib.fm_attention_prefill_static_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
-                                              out.data_ptr(), B, T, window, scale, _VALUE_CODES[out.dtype],
+                                              out.data_ptr(), B, T, window, scale, _VALUE_CODES[out.dtype] | in_flag,
                                               _status_ptr(status, x), _stream())
     _native.check(rc, "fm_attention_prefill_static_bf16")
     return out
@@ -178,9 +187,7 @@ def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_
     lib = _native.load()
     _need(x.dim() == 2, "x must be [S, 512]")
     S = x.shape[0]
-    _check_frames(x, "x", torch.bfloat16)
-    _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
-          and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+    in_flag = _check_projection_inputs(x, w_qkv)
     bstride = 0 if cos.shape[0] == 1 else HEAD_DIM
     _check_tables(cos, sin, S, 1)
     _need(ring_k.dim() == 4 and ring_k.shape[0] == S and ring_k.shape[1] == HEADS and ring_k.shape[3] == HEAD_DIM,
@@ -193,7 +200,7 @@ def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_
         _need(stream_pos.is_cuda and stream_pos.dtype == torch.int32 and stream_pos.numel() == S
               and stream_pos.is_contiguous(), "stream_pos must be a contiguous CUDA int32 [S]")
     if q_workspace is None:
-        q_workspace = torch.empty_like(x)
+        q_workspace = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
     _check_frames(q_workspace, "q workspace", torch.bfloat16, S)
     if out is None:
         out = torch.empty((S, HIDDEN), dtype=torch.float32, device=x.device)
@@ -201,7 +208,7 @@ def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_
           "out must be contiguous float32 [S, 512]")
     rc = lib.fm_decode_step_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
                                  _ptr(stream_pos), int(position), q_workspace.data_ptr(), ring_k.data_ptr(),
-                                 ring_v.data_ptr(), out.data_ptr(), S, slots, scale, _VALUE_CODES[ring_v.dtype],
+                                 ring_v.data_ptr(), out.data_ptr(), S, slots, scale, _VALUE_CODES[ring_v.dtype] | in_flag,
                                  _status_ptr(status, x), _stream())
     _native.check(rc, "fm_decode_step_bf16")
     return out
@@ -218,16 +225,15 @@ class DecodePlan:
         cos = torch.zeros(1, 1, HEAD_DIM, device=x.device)
         # run the full validation once through the checked entry point's helpers
         _need(x.dim() == 2, "x must be [S, 512]")
-        _check_frames(x, "x", torch.bfloat16)
-        _need(w_qkv.is_cuda and w_qkv.dtype == torch.bfloat16 and w_qkv.is_contiguous()
-              and tuple(w_qkv.shape) == (3 * HIDDEN, HIDDEN), "w_qkv must be contiguous bf16 [1536, 512]")
+        in_flag = _check_projection_inputs(x, w_qkv)
         _check_tables(cos, cos, S, 1)
         _need(ring_k.dim() == 4 and ring_k.shape[0] == S and ring_k.shape[1] == HEADS and ring_k.shape[3] == HEAD_DIM
               and ring_k.is_cuda and ring_k.dtype == torch.bfloat16 and ring_k.is_contiguous(),
               "ring_k must be contiguous bf16 [S, 8, slots, 64]")
         _need(ring_v.is_cuda and ring_v.dtype in _VALUE_CODES and ring_v.is_contiguous() and ring_v.shape == ring_k.shape,
               "ring_v must match ring_k (float16 or bfloat16)")
-        self.q_workspace = torch.empty_like(x) if q_workspace is None else q_workspace
+        self.q_workspace = (torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if q_workspace is None
+                            else q_workspace)
         _check_frames(self.q_workspace, "q workspace", torch.bfloat16, S)
         self.out = torch.empty((S, HIDDEN), dtype=torch.float32, device=x.device) if out is None else out
         _need(self.out.is_cuda and self.out.dtype == torch.float32 and self.out.is_contiguous()
@@ -235,7 +241,7 @@ class DecodePlan:
         self._keep = (x, w_qkv, ring_k, ring_v, status)
         self._args_head = (x.data_ptr(), w_qkv.data_ptr())
         self._args_tail = (self.q_workspace.data_ptr(), ring_k.data_ptr(), ring_v.data_ptr(), self.out.data_ptr(), S,
-                           ring_k.shape[2], float(scale), _VALUE_CODES[ring_v.dtype], _status_ptr(status, x))
+                           ring_k.shape[2], float(scale), _VALUE_CODES[ring_v.dtype] | in_flag, _status_ptr(status, x))
 
     def step(self, position: int, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         """``cos, sin``: contiguous float32 ``[1, 1, 64]`` tables of the new frame's position."""

@@ -11,8 +11,10 @@
  *     a TMA / tensor-core completion barrier runs out writes a code >= 101 there and finishes early.
  *     Read it back with fm_read_status().
  *   - geometry of the tensor-core entry points is Mimi's: hidden 512, 8 heads of 64.
- *   - value_dtype: 0 = BF16, 1 = FP16: storage type of V, of the softmax probabilities fed to the
- *     tensor core, and of the prefill output.  Q and K are always BF16.
+ *   - value_dtype: bit 0 selects the storage type of V, of the softmax probabilities fed to the tensor
+ *     core and of the prefill output: 0 = BF16, 1 = FP16.  Q and K are always BF16.  In the entry points
+ *     that contain the projection, bit 1 (value 2) says that x and w_qkv hold FP16 instead of BF16 (same
+ *     tensor-core rate, 8x finer rounding of FP32 activations and weights; needs |values| < 65504).
  *
  * Tensors named "frames" are [B, T, 512] row-major (heads are 64-column slices), which is the
  * memory layout behind the reference's [B, 8, T, 64] strided views (src/fast_mimi/model.py:1897-1911).

@@ -38,7 +38,7 @@ def golden():
     return load_golden
 
 
-def regen_projections(seed: int, hidden: int = 512, std: float = 0.02):
+def regen_projections(seed: int, hidden: int = 512, std: float = 0.02, bf16_inputs: bool = True):
     """Rebuild the seeded weights of ``tests/golden/make_golden.py`` without the reference: four
     bias-free Linear(hidden, hidden) constructed in q,k,v,o order (their default init consumes the
     RNG), re-initialised N(0, std^2) in the same order; q/k/v weights rounded to BF16-representable
@@ -48,13 +48,19 @@ def regen_projections(seed: int, hidden: int = 512, std: float = 0.02):
     for lin in lins:
         torch.nn.init.normal_(lin.weight, std=std)
     wq, wk, wv, wo = (lin.weight.detach() for lin in lins)
+    if not bf16_inputs:
+        return wq, wk, wv, wo
     return wq.bfloat16().float(), wk.bfloat16().float(), wv.bfloat16().float(), wo
 
 
-def regen_attention_layer(seed: int, b: int, t: int, hidden: int = 512, std: float = 0.02):
-    """Weights as ``regen_projections`` then x ~ N(0,1) rounded to BF16-representable values."""
-    wq, wk, wv, wo = regen_projections(seed, hidden, std)
-    x = torch.randn(b, t, hidden).bfloat16().float()
+def regen_attention_layer(seed: int, b: int, t: int, hidden: int = 512, std: float = 0.02,
+                          bf16_inputs: bool = True):
+    """Weights as ``regen_projections`` then x ~ N(0,1), rounded to BF16-representable values unless the
+    fixture was generated from full FP32 inputs."""
+    wq, wk, wv, wo = regen_projections(seed, hidden, std, bf16_inputs)
+    x = torch.randn(b, t, hidden)
+    if bf16_inputs:
+        x = x.bfloat16().float()
     return x, wq, wk, wv, wo
 
 

@@ -225,6 +225,8 @@ if __name__ == "__main__":
     attention_layer("tiny_attention_layer.npz", tiny_config(), 2, 21, seed=11)
     attention_layer("attention_layer_T250.npz", MimiConfig(), 2, 250, seed=1,
                     rows=sorted(set(list(range(0, 250, 17)) + [127, 128, 249])), bf16_inputs=True)
+    attention_layer("attention_layer_T250_fp32.npz", MimiConfig(), 2, 250, seed=3,
+                    rows=sorted(set(list(range(0, 250, 17)) + [127, 128, 249])), bf16_inputs=False)
     attention_layer("attention_layer_T313.npz", MimiConfig(), 1, 313, seed=2,
                     rows=sorted(set(list(range(0, 313, 23)) + [249, 250, 251, 312])), bf16_inputs=True)
     cached_streams("tiny_cached_chunks.npz", tiny_config(), 2, [4, 4, 4, 4, 4, 1, 1, 3, 9, 1], seed=12)

@@ -131,6 +131,26 @@ def test_attention_module_matches_reference_layer(name):
     assert O.rel_l2(out[:, g["rows"]].cpu(), g["out"]) < TOL
 
 
+def test_attention_module_with_full_fp32_weights_and_activations():
+    """The drop-in scenario: an FP32 model whose weights and activations are NOT BF16-representable.  The
+    module feeds the tensor core FP16 copies of x and W (BF16 copies alone would cost 2.4e-3)."""
+    import fast_mimi_b200 as fm
+    g = load_golden("attention_layer_T250_fp32.npz")
+    m = fm.MimiAttentionB200().cuda()
+    x, wq, wk, wv, wo = regen_attention_layer(int(g["seed"]), int(g["b"]), int(g["t"]), bf16_inputs=False)
+    assert torch.equal(x[0, :2, :8], g["x_probe"]) and torch.equal(wq[:2, :8], g["wq_probe"])
+    with torch.no_grad():
+        for lin, w in zip((m.q_proj, m.k_proj, m.v_proj, m.o_proj), (wq, wk, wv, wo)):
+            lin.weight.copy_(w)
+    cos, sin = O.rope_tables(torch.arange(x.shape[1]))
+    out, _ = m(x.cuda(), None, None, (cos.cuda()[None], sin.cuda()[None]))
+    assert O.rel_l2(out[:, g["rows"]].cpu(), g["out"]) < TOL
+    # the same module told to use BF16 inputs lands above the tolerance, which is why FP16 is the default
+    m.input_dtype = torch.bfloat16
+    out_bf16, _ = m(x.cuda(), None, None, (cos.cuda()[None], sin.cuda()[None]))
+    assert 2e-3 < O.rel_l2(out_bf16[:, g["rows"]].cpu(), g["out"]) < 6e-3
+
+
 def test_streaming_decode_260_steps_matches_reference():
     """260 one-frame steps through the KV ring (fills, then wraps at step 250) vs the reference's
     MimiKVCache + SDPA outputs; the ring must hold the same rows as the reference cache."""

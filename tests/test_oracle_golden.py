@@ -46,9 +46,10 @@ def test_tiny_attention_layer_matches_reference():
 
 
 def test_full_size_attention_layers_match_reference():
-    for name in ("attention_layer_T250.npz", "attention_layer_T313.npz"):
+    for name in ("attention_layer_T250.npz", "attention_layer_T313.npz", "attention_layer_T250_fp32.npz"):
         g = load_golden(name)
-        x, wq, wk, wv, wo = regen_attention_layer(int(g["seed"]), int(g["b"]), int(g["t"]))
+        x, wq, wk, wv, wo = regen_attention_layer(int(g["seed"]), int(g["b"]), int(g["t"]),
+                                                  bf16_inputs="fp32" not in name)
         assert torch.equal(x[0, :2, :8], g["x_probe"]) and torch.equal(wq[:2, :8], g["wq_probe"])
         out = O.attention_forward(x, wq, wk, wv, wo)
         assert (out[:, g["rows"]] - g["out"]).abs().max() < TOL
