@@ -3,23 +3,21 @@
 // [B, T, 512], output [B, T, 512]; replaces the masked SDPA call of the reference
 // (src/fast_mimi/model.py:1860-1868 with the band of src/fast_mimi/model.py:1672-1676).
 //
-// A persistent CTA takes (clip, head) items.  All of an item's operands — Q, K, V for both 128-frame
-// halves, 96 KB — arrive in one TMA batch, and the next item's batch is in flight while the current one
-// is computed (two 96 KB buffers).  The three score tiles of the causal band
-//     S00 = rows 0-127 x keys 0-127,  S10 = rows 128-255 x keys 0-127,  S11 = rows 128-255 x keys 128-255
-// are issued back to back into 384 TMEM columns, so a softmax row sees all of its scores at once: one
-// pass for the row maximum, one for the probabilities, no running rescale, and the tensor core
-// accumulates P V for both key tiles directly in TMEM (2 x 64 columns).
-//
-// Twelve softmax warps, three per SM sub-partition, each owning one tile:
-//     warps 0-3   S00   (frames permuted so that warp w holds frames 96-32w .. 127-32w)
-//     warps 4-7   S10   (rows 128-255, keys 0-127; also normalise, stage and store the rows' output)
-//     warps 8-11  S11   (rows 128-255, keys 128-255)
-// The causal diagonal gives warp w of S00 4-w visible 32-key groups and warp w of S11 w+1, so every
-// sub-partition handles nine groups.  The S10 / S11 warps of a row exchange their partial maximum and
-// sum through shared memory (named barriers).  P tiles overwrite the item's dead Q / K tiles (plus one
-// extra 32 KB tile for P11); outputs are staged in tiles that are dead by then and leave through TMA
-// stores.  Warp 12: TMA loads + MMA issue.
+// A persistent CTA takes (clip, head) items; an item's Q, K, V for both 128-frame halves (96 KB) arrive
+// in one TMA batch and the next item's batch is in flight meanwhile (two buffers).  The causal band of an
+// item is three 128 x 128 score tiles, handled as three uniform JOBS:
+//     kind 0: rows 0-127 x keys 0-127     kind 1: rows 128-255 x keys 0-127     kind 2: rows 128-255 x keys 128-255
+// Tensor memory is four 128-column SLOTS; job g runs in slot g % 4 with softmax team g % 4 (four warps,
+// one query row per thread).  In a slot, S = Q K^T (FP32, 128 columns) is turned IN PLACE into the 16-bit
+// probabilities P (columns 0-63), which the tensor core reads straight from tensor memory as the A operand
+// of O = P V; O (FP32) lands in columns 64-127 of the slot.  So there is no shared-memory round trip for P,
+// and up to four jobs are in flight: while one team exponentiates, the tensor core works on other slots.
+// Rows 128-255 need both of their tiles: the two teams exchange row maxima (and later row sums) through
+// shared memory, use one common maximum, and the tensor core accumulates both P V products into the
+// kind-2 slot.  The causal diagonal leaves warp w of a kind-0 job 4-w visible 32-key groups (its frames are
+// loaded in permuted order) and warp w of a kind-2 job w+1, which balances the four SM sub-partitions.
+// Outputs are normalised, staged in the item's dead Q tiles and leave through TMA stores.
+// Warps 0-15: softmax teams.  Warp 16: TMA loads + MMA issue (whatever is ready next is issued).
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -31,98 +29,107 @@ constexpr int kD = 64;
 constexpr int kTileBytes = kTile * kD * 2;          // 16 KB
 constexpr int kSlabBytes = 32 * 128;                // 32 rows x 64 x 16 bit
 constexpr int kItemBytes = 6 * kTileBytes;          // Q0 Q1 K0 K1 V0 V1
-constexpr int kSoftmaxWarps = 12;
+constexpr int kSlots = 4;
+constexpr int kSoftmaxWarps = 4 * kSlots;
 constexpr int kThreads = (kSoftmaxWarps + 1) * 32;
-constexpr int kTmemCols = 512;                      // S00 | S10 | S11 | O0 | O1
-constexpr uint32_t kS00 = 0, kS10 = 128, kS11 = 256, kO0 = 384, kO1 = 448;
+constexpr int kTmemCols = 128 * kSlots;
+constexpr uint32_t kPCol = 0, kOCol = 64;           // inside a slot: P over the consumed S, then O
 
 struct Shared {
   uint64_t load_full[2];
-  uint64_t buf_free[2];    // the P V products that read a buffer have completed
-  uint64_t out_done[2];    // the output staged in a buffer has been read by its TMA stores
-  uint64_t s_full[2];      // [0]: S00; [1]: S10 and S11
-  uint64_t p_full[2];      // [0]: P00 written (4 warps); [1]: P10 and P11 written (8 warps)
-  uint64_t o_full[2];
+  uint64_t pv_done_a[2];   // P V of the item's kind-0 job has completed (reads V0)
+  uint64_t pv_done_b[2];   // P V of the item's kind-1 and kind-2 jobs have completed (read V0, V1)
+  uint64_t out_done[2];    // the outputs staged in the item's Q tiles have been read by their TMA stores
+  uint64_t s_full[kSlots];
+  uint64_t p_full[kSlots];
+  uint64_t o_full[kSlots];
+  uint64_t slot_free[kSlots];   // the team is done with the slot's tensor memory (tested for kinds 0 and 2)
+  uint64_t xm_full[4];     // row maxima of a kind-1 / kind-2 pair are both published (8 warps)
+  uint64_t xl_full[4];     // row sums of the kind-1 job are published (4 warps)
   uint32_t tmem_base;
   CtaCtl ctl;
-  float xm[kTile][2];      // partial row maxima of S10 / S11
-  float xl[kTile];         // partial row sums of S11
+  float xm[4][kTile][2];
+  float xl[4][kTile];
 };
-constexpr int kSmemBytes = 1024 + 2 * kItemBytes + 2 * kTileBytes + static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
+constexpr int kSmemBytes = 1024 + 2 * kItemBytes + static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
 
-// Row maximum of the visible raw scores of one 128 x 128 tile (this thread's row).
-__device__ __forceinline__ float tile_row_max(uint32_t s_addr, int i, int w_row0, int k0, int window) {
-  const int vis_lo = i - window + 1 - k0, vis_hi = i - k0;
-  const int any_lo = w_row0 - window + 1 - k0, any_hi = w_row0 + 31 - k0;   // seen by at least one row of the warp
-  const int all_lo = w_row0 + 31 - window + 1 - k0, all_hi = w_row0 - k0;   // seen by every row of the warp
+// Which 32-column groups of a 128 x 128 score tile matter to a warp whose rows are frames
+// w_row0 .. w_row0+31, against keys k0 .. k0+127, under the causal window.
+struct GroupVis {
+  int vis_lo, vis_hi;   // this thread's visible columns
+  int any_lo, any_hi;   // columns seen by at least one row of the warp
+  int all_lo, all_hi;   // columns seen by every row of the warp
+  __device__ __forceinline__ GroupVis(int i, int w_row0, int k0, int window)
+      : vis_lo(i - window + 1 - k0), vis_hi(i - k0), any_lo(w_row0 - window + 1 - k0), any_hi(w_row0 + 31 - k0),
+        all_lo(w_row0 + 31 - window + 1 - k0), all_hi(w_row0 - k0) {}
+  __device__ __forceinline__ bool skip(int c0) const { return c0 > any_hi || c0 + 31 < any_lo; }
+  __device__ __forceinline__ bool full(int c0) const { return c0 >= all_lo && c0 + 31 <= all_hi; }
+};
+
+// Row maximum of the visible raw scores of a tile (this thread's row).
+__device__ __forceinline__ float tile_row_max(uint32_t s_addr, const GroupVis& g) {
   float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
   for (int c0 = 0; c0 < kTile; c0 += 32) {
-    if (c0 > any_hi || c0 + 31 < any_lo) continue;
+    if (g.skip(c0)) continue;
     uint32_t s[32];
     tmem_ld32(s_addr + c0, s);
     tmem_ld_wait();
-    if (c0 >= all_lo && c0 + 31 <= all_hi) {
+    if (g.full(c0)) {
 #pragma unroll
       for (int cc = 0; cc < 32; ++cc) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
     } else {
 #pragma unroll
       for (int cc = 0; cc < 32; ++cc)
-        if (c0 + cc >= vis_lo && c0 + cc <= vis_hi) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
+        if (c0 + cc >= g.vis_lo && c0 + cc <= g.vis_hi) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
     }
   }
   return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
 }
 
-// exp2(scale * s - m) of one tile row -> 16-bit P tile (two swizzled 64-key halves); returns the row sum.
+// exp2(scale * s - m) of this thread's tile row, written over the consumed scores as packed 16-bit pairs
+// (32 keys -> 16 columns, ascending, so a group's P never lands on scores that are still to be read).
+// Returns the row sum.
 template <typename VT>
-__device__ __forceinline__ float tile_row_probs(uint32_t s_addr, uint8_t* p_lo, uint8_t* p_hi, int r, int i, int w_row0,
-                                                int k0, int window, float scale_log2e, float m_use) {
-  const int vis_lo = i - window + 1 - k0, vis_hi = i - k0;
-  const int any_lo = w_row0 - window + 1 - k0, any_hi = w_row0 + 31 - k0;
-  const int all_lo = w_row0 + 31 - window + 1 - k0, all_hi = w_row0 - k0;
+__device__ __forceinline__ float tile_row_probs(uint32_t s_addr, uint32_t p_addr, const GroupVis& g, float scale_log2e,
+                                                float m_use) {
   float l[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
   for (int c0 = 0; c0 < kTile; c0 += 32) {
-    uint8_t* half_base = (c0 >> 6) == 0 ? p_lo : p_hi;
-    const int chunk0 = (c0 & 63) >> 3;
-    if (c0 > any_hi || c0 + 31 < any_lo) {
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc)
-        *reinterpret_cast<uint4*>(half_base + sw128_offset(r, chunk0 + cc)) = make_uint4(0u, 0u, 0u, 0u);
-      continue;
-    }
-    uint32_t s[32];
-    tmem_ld32(s_addr + c0, s);
-    tmem_ld_wait();
     uint32_t pk[16];
-    if (c0 >= all_lo && c0 + 31 <= all_hi) {
+    if (g.skip(c0)) {
 #pragma unroll
-      for (int cc = 0; cc < 32; cc += 2) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc]), scale_log2e, -m_use));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc + 1]), scale_log2e, -m_use));
-        pk[cc / 2] = Pack16<VT>::pack(p0, p1);
-        l[(cc >> 1) & 3] += p0 + p1;
-      }
+      for (int j = 0; j < 16; ++j) pk[j] = 0u;
     } else {
+      uint32_t s[32];
+      tmem_ld32(s_addr + c0, s);
+      tmem_ld_wait();
+      if (g.full(c0)) {
 #pragma unroll
-      for (int cc = 0; cc < 32; cc += 2) {
-        float p[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const bool vis = c0 + cc + e >= vis_lo && c0 + cc + e <= vis_hi;
-          p[e] = vis ? ex2_approx(fmaf(__uint_as_float(s[cc + e]), scale_log2e, -m_use)) : 0.f;
+        for (int cc = 0; cc < 32; cc += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc]), scale_log2e, -m_use));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc + 1]), scale_log2e, -m_use));
+          pk[cc / 2] = Pack16<VT>::pack(p0, p1);
+          l[(cc >> 1) & 3] += p0 + p1;
         }
-        pk[cc / 2] = Pack16<VT>::pack(p[0], p[1]);
-        l[(cc >> 1) & 3] += p[0] + p[1];
+      } else {
+#pragma unroll
+        for (int cc = 0; cc < 32; cc += 2) {
+          float p[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const bool vis = c0 + cc + e >= g.vis_lo && c0 + cc + e <= g.vis_hi;
+            p[e] = vis ? ex2_approx(fmaf(__uint_as_float(s[cc + e]), scale_log2e, -m_use)) : 0.f;
+          }
+          pk[cc / 2] = Pack16<VT>::pack(p[0], p[1]);
+          l[(cc >> 1) & 3] += p[0] + p[1];
+        }
       }
     }
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc)
-      *reinterpret_cast<uint4*>(half_base + sw128_offset(r, chunk0 + cc)) =
-          make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
+    tmem_st16(p_addr + (c0 >> 1), pk);
   }
+  tmem_st_wait();
   return (l[0] + l[1]) + (l[2] + l[3]);
 }
 
@@ -144,10 +151,6 @@ __device__ __forceinline__ void stage_output_row(uint32_t o_addr, uint8_t* slab,
     }
   }
 }
-
-__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
 }  // namespace clip
 
 template <typename VT>
@@ -161,8 +164,7 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_p11 = smem + 2 * kItemBytes;
-  Shared* sh = reinterpret_cast<Shared*>(smem_p11 + 2 * kTileBytes);
+  Shared* sh = reinterpret_cast<Shared*>(smem + 2 * kItemBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -170,13 +172,18 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh->load_full[i], 1);
-      mbar_init(&sh->buf_free[i], 1);
+      mbar_init(&sh->pv_done_a[i], 1);
+      mbar_init(&sh->pv_done_b[i], 1);
       mbar_init(&sh->out_done[i], 8);
-      mbar_init(&sh->s_full[i], 1);
-      mbar_init(&sh->o_full[i], 1);
     }
-    mbar_init(&sh->p_full[0], 4);
-    mbar_init(&sh->p_full[1], 8);
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(&sh->s_full[i], 1);
+      mbar_init(&sh->p_full[i], 4);
+      mbar_init(&sh->o_full[i], 1);
+      mbar_init(&sh->slot_free[i], 4);
+      mbar_init(&sh->xm_full[i], 8);
+      mbar_init(&sh->xl_full[i], 4);
+    }
     sh->ctl.abort = 0;
     fence_mbar_init();
   }
@@ -190,6 +197,7 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const uint32_t tmem_base = sh->tmem_base;
   CtaCtl* ctl = &sh->ctl;
   const int n_local = (n_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int n_jobs = 3 * n_local;
 
   if (warp == kSoftmaxWarps) {
     // ------------------------------------------------------------ TMA loads + MMA issue
@@ -214,153 +222,151 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       };
       constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
-      if (n_local > 0) load_item(0);
-      for (int n = 0; n < n_local; ++n) {
-        const int b = n & 1;
-        uint8_t* base = smem + b * kItemBytes;
-        mbar_wait(&sh->load_full[b], static_cast<uint32_t>(n >> 1) & 1u, ctl, status, kErrWaitTma);
-        tc_fence_after_sync();
-        const uint64_t q0 = umma_desc_sw128(smem_u32(base)), q1 = umma_desc_sw128(smem_u32(base + kTileBytes));
-        const uint64_t k0 = umma_desc_sw128(smem_u32(base + 2 * kTileBytes));
-        const uint64_t k1 = umma_desc_sw128(smem_u32(base + 3 * kTileBytes));
+      auto slot_addr = [&](int g) { return tmem_base + static_cast<uint32_t>((g & 3) * kTile); };
+      auto job_phase = [](int g) { return static_cast<uint32_t>(g >> 2) & 1u; };
+      // O (+)= P V for one job: A = P from tensor memory (8 columns per 16 keys), B = V (MN-major, 2 KB per 16 keys).
+      auto issue_pv = [&](int g_p, int g_o, const uint8_t* v_tile, bool accumulate) {
+        const uint64_t v = umma_desc_sw128(smem_u32(v_tile));
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(tmem_base + kS00, q0 + 2u * ks, k0 + 2u * ks, idesc_qk, ks != 0);
-        tc_commit(&sh->s_full[0]);
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(tmem_base + kS10, q1 + 2u * ks, k0 + 2u * ks, idesc_qk, ks != 0);
-#pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(tmem_base + kS11, q1 + 2u * ks, k1 + 2u * ks, idesc_qk, ks != 0);
-        tc_commit(&sh->s_full[1]);
-        if (n + 1 < n_local) {
-          if (n >= 1) {
-            // The other buffer held item n-1: its P V reads and its staged output must be finished.
-            const uint32_t ph = static_cast<uint32_t>((n - 1) >> 1) & 1u;
-            mbar_wait(&sh->buf_free[b ^ 1], ph, ctl, status, kErrWaitMma);
-            mbar_wait(&sh->out_done[b ^ 1], ph, ctl, status, kErrWaitConsumer);
+        for (int ks = 0; ks < kTile / 16; ++ks)
+          tc_mma_ts(slot_addr(g_o) + kOCol, slot_addr(g_p) + kPCol + 8u * ks, v + static_cast<uint64_t>(ks) * 128u, idesc_pv,
+                    (accumulate || ks != 0) ? 1u : 0u);
+      };
+      // nl: next item to load.  ready: items whose load has been seen complete.  gq: next job whose scores
+      // are issued.  pa / pb: next item whose kind-0 / kind-1+2 P V is issued.
+      int nl = 0, ready = 0, gq = 0, pa = 0, pb = 0;
+      unsigned long long t_idle = 0;
+      uint32_t idle_spins = 0;
+      while (pa < n_local || pb < n_local) {
+        bool progress = false;
+        if (nl < n_local) {
+          bool ok = true;
+          if (nl >= 2) {
+            const int b = nl & 1;
+            const uint32_t ph = static_cast<uint32_t>((nl - 2) >> 1) & 1u;
+            ok = mbar_try_wait(&sh->pv_done_a[b], ph) && mbar_try_wait(&sh->pv_done_b[b], ph) &&
+                 mbar_try_wait(&sh->out_done[b], ph);
           }
-          load_item(n + 1);
+          if (ok) { load_item(nl); ++nl; progress = true; }
         }
-        const uint64_t v0 = umma_desc_sw128(smem_u32(base + 4 * kTileBytes));
-        const uint64_t v1 = umma_desc_sw128(smem_u32(base + 5 * kTileBytes));
-        // rows 0-127: O0 = P00 V0 (P00 lives where Q0, Q1 were)
-        mbar_wait(&sh->p_full[0], static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitConsumer);
-        tc_fence_after_sync();
+        if (ready < nl && mbar_try_wait(&sh->load_full[ready & 1], static_cast<uint32_t>(ready >> 1) & 1u)) {
+          ++ready; progress = true;
+        }
+        if (gq < n_jobs && gq / 3 < ready) {
+          // The slot's previous job (gq-4) must be out of it: a kind-1 job once its P V has been issued (the
+          // tensor core runs in order), the others once their team has read O.
+          bool free_slot = true;
+          if (gq >= 4) {
+            const int gp = gq - 4;
+            free_slot = (gp % 3 == 1) ? (pb > gp / 3) : mbar_try_wait(&sh->slot_free[gp & 3], job_phase(gp));
+          }
+          if (free_slot) {
+            tc_fence_after_sync();
+            const int n = gq / 3, kind = gq % 3;
+            const uint8_t* base = smem + (n & 1) * kItemBytes;
+            const uint64_t qd = umma_desc_sw128(smem_u32(base + (kind == 0 ? 0 : 1) * kTileBytes));
+            const uint64_t kd = umma_desc_sw128(smem_u32(base + (kind == 2 ? 3 : 2) * kTileBytes));
 #pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-          const uint64_t p = umma_desc_sw128(smem_u32(base + (ks >> 2) * kTileBytes)) + 2u * (ks & 3);
-          tc_mma_ss(tmem_base + kO0, p, v0 + static_cast<uint64_t>(ks) * 128u, idesc_pv, ks != 0);
+            for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(slot_addr(gq), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
+            tc_commit(&sh->s_full[gq & 3]);
+            ++gq; progress = true;
+          }
         }
-        tc_commit(&sh->o_full[0]);
-        // rows 128-255: O1 = P10 V0 + P11 V1 (P10 where K0, K1 were; P11 in the extra tile)
-        mbar_wait(&sh->p_full[1], static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitConsumer);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-          const uint64_t p = umma_desc_sw128(smem_u32(base + (2 + (ks >> 2)) * kTileBytes)) + 2u * (ks & 3);
-          tc_mma_ss(tmem_base + kO1, p, v0 + static_cast<uint64_t>(ks) * 128u, idesc_pv, ks != 0);
+        if (pa < n_local && gq > 3 * pa && mbar_try_wait(&sh->p_full[(3 * pa) & 3], job_phase(3 * pa))) {
+          tc_fence_after_sync();
+          const uint8_t* base = smem + (pa & 1) * kItemBytes;
+          issue_pv(3 * pa, 3 * pa, base + 4 * kTileBytes, false);
+          tc_commit(&sh->o_full[(3 * pa) & 3]);
+          tc_commit(&sh->pv_done_a[pa & 1]);
+          ++pa; progress = true;
         }
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks) {
-          const uint64_t p = umma_desc_sw128(smem_u32(smem_p11 + (ks >> 2) * kTileBytes)) + 2u * (ks & 3);
-          tc_mma_ss(tmem_base + kO1, p, v1 + static_cast<uint64_t>(ks) * 128u, idesc_pv, 1u);
+        if (pb < n_local && gq > 3 * pb + 2 && mbar_try_wait(&sh->p_full[(3 * pb + 1) & 3], job_phase(3 * pb + 1)) &&
+            mbar_try_wait(&sh->p_full[(3 * pb + 2) & 3], job_phase(3 * pb + 2))) {
+          tc_fence_after_sync();
+          const uint8_t* base = smem + (pb & 1) * kItemBytes;
+          issue_pv(3 * pb + 1, 3 * pb + 2, base + 4 * kTileBytes, false);   // P10 V0
+          issue_pv(3 * pb + 2, 3 * pb + 2, base + 5 * kTileBytes, true);    // + P11 V1
+          tc_commit(&sh->o_full[(3 * pb + 2) & 3]);
+          tc_commit(&sh->o_full[(3 * pb + 1) & 3]);   // nobody waits on it; one completion per slot use
+          tc_commit(&sh->pv_done_b[pb & 1]);
+          ++pb; progress = true;
         }
-        tc_commit(&sh->o_full[1]);
-        tc_commit(&sh->buf_free[b]);
+        if (progress) {
+          idle_spins = 0;
+        } else if ((++idle_spins & 255u) == 0u) {
+          // Bounded: give up after kWaitLimitNs without any step becoming possible.
+          if (ctl->abort) break;
+          const unsigned long long now = global_timer_ns();
+          if (idle_spins == 256u) t_idle = now;
+          if (now - t_idle > kWaitLimitNs) {
+            ctl->abort = 1;
+            if (status != nullptr) atomicMax(status, static_cast<int>(kErrWaitConsumer));
+            break;
+          }
+        }
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax warps
-    const int role = warp >> 2;               // 0: S00, 1: S10, 2: S11
+    // ------------------------------------------------------------ softmax teams
+    const int team = warp >> 2;               // == slot
     const int lg = warp & 3;                  // TMEM lane group
     const int r = lg * 32 + lane;             // row of the tile == TMEM lane
-    const uint32_t lane_sel = static_cast<uint32_t>(lg * 32) << 16;
-    // First frame held by this warp, and this thread's frame.
-    const int w_row0 = role == 0 ? (3 - lg) * 32 : kTile + lg * 32;
-    const int i = w_row0 + lane;
-    for (int n = 0; n < n_local; ++n) {
+    const uint32_t slot = tmem_base + static_cast<uint32_t>(team * kTile) + (static_cast<uint32_t>(lg * 32) << 16);
+    for (int g = team; g < n_jobs; g += kSlots) {
+      const int n = g / 3, kind = g % 3, b = n & 1, x = n & 3;
+      const uint32_t ph = static_cast<uint32_t>(g >> 2) & 1u;      // this slot's use number
+      const uint32_t xph = static_cast<uint32_t>(n >> 2) & 1u;     // this exchange buffer's use number
       const int item = blockIdx.x + n * gridDim.x;
-      const int c = item >> 3, h = item & 7, b = n & 1;
-      const uint32_t ph = static_cast<uint32_t>(n) & 1u;
+      const int c = item >> 3, h = item & 7;
       uint8_t* base = smem + b * kItemBytes;
-      if (role == 0) {
-        mbar_wait(&sh->s_full[0], ph, ctl, status, kErrWaitMma);
-        tc_fence_after_sync();
-        const float m_raw = tile_row_max(tmem_base + lane_sel + kS00, i, w_row0, 0, window);
-        const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
-        // The second half of P00 overwrites Q1, which S10 / S11 still read until s_full[1].
-        mbar_wait(&sh->s_full[1], ph, ctl, status, kErrWaitMma);
-        const float l_row = tile_row_probs<VT>(tmem_base + lane_sel + kS00, base, base + kTileBytes, r, i, w_row0, 0,
-                                               window, scale_log2e, m_use);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->p_full[0]);
+      const int w_row0 = kind == 0 ? (3 - lg) * 32 : kTile + lg * 32;   // first frame held by this warp
+      const int i = w_row0 + lane;
+      const GroupVis vis(i, w_row0, kind == 2 ? kTile : 0, window);
 
-        mbar_wait(&sh->o_full[0], ph, ctl, status, kErrWaitMma);
-        tc_fence_after_sync();
-        uint8_t* slab = base + lg * kSlabBytes;                 // inside the dead Q0 tile
-        stage_output_row<VT>(tmem_base + lane_sel + kO0, slab, lane, 1.f / l_row);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
+      mbar_wait(&sh->s_full[team], ph, ctl, status, kErrWaitMma);
+      tc_fence_after_sync();
+      float m_raw = tile_row_max(slot, vis);
+      if (kind != 0) {
+        sh->xm[x][r][kind - 1] = m_raw;
         __syncwarp();
-        if (lane == 0) {
-          if (w_row0 < T) {                                     // frames past T are clipped by the map
-            tma_store_3d(&tmap_out, slab, h * kD, w_row0, c);
-            bulk_commit_group();
-            bulk_wait_group_read<0>();
-          }
-          mbar_arrive(&sh->out_done[b]);
+        if (lane == 0) mbar_arrive(&sh->xm_full[x]);
+        mbar_wait(&sh->xm_full[x], xph, ctl, status, kErrWaitConsumer);
+        m_raw = fmaxf(m_raw, sh->xm[x][r][2 - kind]);
+      }
+      const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
+      float l_row = tile_row_probs<VT>(slot, slot + kPCol, vis, scale_log2e, m_use);
+      if (kind == 1) sh->xl[x][r] = l_row;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sh->p_full[team]);
+        if (kind == 1) {
+          mbar_arrive(&sh->xl_full[x]);
+          mbar_arrive(&sh->slot_free[team]);   // keeps the barrier's phase in step with the slot's use count
         }
-      } else if (role == 1) {
-        mbar_wait(&sh->s_full[1], ph, ctl, status, kErrWaitMma);
-        tc_fence_after_sync();
-        const float m_a = tile_row_max(tmem_base + lane_sel + kS10, i, w_row0, 0, window);
-        sh->xm[r][0] = m_a;
-        named_bar_sync(1 + lg, 64);
-        const float m_raw = fmaxf(m_a, sh->xm[r][1]);
-        const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
-        const float l_a = tile_row_probs<VT>(tmem_base + lane_sel + kS10, base + 2 * kTileBytes, base + 3 * kTileBytes, r,
-                                             i, w_row0, 0, window, scale_log2e, m_use);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        // The S11 warp's row sums are read before this warp's arrival lets the next item start, so the
-        // next item's sums cannot overwrite them first.
-        named_bar_sync(5 + lg, 64);
-        const float l_row = l_a + sh->xl[r];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->p_full[1]);
+      }
+      if (kind == 1) continue;                 // the kind-2 team finishes rows 128-255
 
-        mbar_wait(&sh->o_full[1], ph, ctl, status, kErrWaitMma);
-        tc_fence_after_sync();
-        uint8_t* slab = base + 2 * kTileBytes + lg * kSlabBytes;   // inside the dead K0 tile
-        stage_output_row<VT>(tmem_base + lane_sel + kO1, slab, lane, 1.f / l_row);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if (w_row0 < T) {
-            tma_store_3d(&tmap_out, slab, h * kD, w_row0, c);
-            bulk_commit_group();
-            bulk_wait_group_read<0>();
-          }
-          mbar_arrive(&sh->out_done[b]);
+      mbar_wait(&sh->o_full[team], ph, ctl, status, kErrWaitMma);
+      tc_fence_after_sync();
+      if (kind == 2) {
+        mbar_wait(&sh->xl_full[x], xph, ctl, status, kErrWaitConsumer);
+        l_row += sh->xl[x][r];
+      }
+      // Staged in the item's Q tile of these rows, which no MMA reads any more (its scores are complete).
+      uint8_t* slab = base + (kind == 0 ? 0 : kTileBytes) + lg * kSlabBytes;
+      stage_output_row<VT>(slot + kOCol, slab, lane, 1.f / l_row);
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sh->slot_free[team]);
+        if (w_row0 < T) {                      // frames past T are clipped by the map
+          tma_store_3d(&tmap_out, slab, h * kD, w_row0, c);
+          bulk_commit_group();
+          bulk_wait_group_read<0>();
         }
-      } else {
-        mbar_wait(&sh->s_full[1], ph, ctl, status, kErrWaitMma);
-        tc_fence_after_sync();
-        const float m_b = tile_row_max(tmem_base + lane_sel + kS11, i, w_row0, kTile, window);
-        sh->xm[r][1] = m_b;
-        named_bar_sync(1 + lg, 64);
-        const float m_raw = fmaxf(m_b, sh->xm[r][0]);
-        const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
-        const float l_b = tile_row_probs<VT>(tmem_base + lane_sel + kS11, smem_p11, smem_p11 + kTileBytes, r, i, w_row0,
-                                             kTile, window, scale_log2e, m_use);
-        sh->xl[r] = l_b;
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->p_full[1]);
-        named_bar_arrive(5 + lg, 64);
+        mbar_arrive(&sh->out_done[b]);
       }
     }
   }
