@@ -74,7 +74,7 @@ class ClockSampler:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
                                           "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
-            time.sleep(0.15)     # let the first sample land before the timed region starts
+            time.sleep(0.6)      # let the first sample land before the timed region starts
         except Exception:
             self.proc = None
         return self

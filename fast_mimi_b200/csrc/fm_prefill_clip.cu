@@ -28,7 +28,6 @@ constexpr int kTile = 128;
 constexpr int kD = 64;
 constexpr int kTileBytes = kTile * kD * 2;          // 16 KB
 constexpr int kSlabBytes = 32 * 128;                // 32 rows x 64 x 16 bit
-constexpr int kItemBytes = 6 * kTileBytes;          // Q0 Q1 K0 K1 V0 V1
 constexpr int kSlots = 4;
 constexpr int kSoftmaxWarps = 4 * kSlots;
 constexpr int kThreads = (kSoftmaxWarps + 1) * 32;
@@ -36,10 +35,13 @@ constexpr int kTmemCols = 128 * kSlots;
 constexpr uint32_t kPCol = 0, kOCol = 64;           // inside a slot: P over the consumed S, then O
 
 struct Shared {
-  uint64_t load_full[2];
+  uint64_t qk_full[2];     // Q0 Q1 K0 K1 of the item in this buffer have landed (64 KB)
+  uint64_t v_full[2];      // V0 V1 of the item in this buffer have landed (32 KB)
+  uint64_t qk_done[2];     // the item's three score products have completed: its Q / K tiles are dead
   uint64_t pv_done_a[2];   // P V of the item's kind-0 job has completed (reads V0)
   uint64_t pv_done_b[2];   // P V of the item's kind-1 and kind-2 jobs have completed (read V0, V1)
-  uint64_t out_done[2];    // the outputs staged in the item's Q tiles have been read by their TMA stores
+  uint64_t out_done_a;     // rows 0-127 of an item: the four staged slabs have been read by their TMA stores
+  uint64_t out_done_b[2];  // rows 128-255 (staged in the item's V1 tile): likewise, per V buffer
   uint64_t s_full[kSlots];
   uint64_t p_full[kSlots];
   uint64_t o_full[kSlots];
@@ -48,12 +50,16 @@ struct Shared {
   uint64_t xl_full[4];     // row sums of the kind-1 job are published (4 warps)
   uint32_t tmem_base;
   CtaCtl ctl;
-  float xm[4][kTile][2];
-  float xl[4][kTile];
+  float xm[4][kTile][2];   // partial row maxima of a kind-1 / kind-2 pair, by item % 4
+  float xl[4][kTile];      // row sums of the kind-1 job
 };
-constexpr int kSmemBytes = 1024 + 2 * kItemBytes + static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
+// Shared memory: two Q/K buffers (4 tiles each), two V buffers (2 tiles each), four 4 KB output slabs for
+// rows 0-127 (rows 128-255 are staged in the item's V1 tile, which only their own P V product reads).
+// Q / K tiles are released as soon as the item's scores exist, V tiles when its P V products are done, so
+// the loads of item n+2 start long before item n has finished.
+constexpr int kQkBytes = 4 * kTileBytes, kVBytes = 2 * kTileBytes, kStageBytes = 4 * kSlabBytes;
+constexpr int kSmemBytes = 1024 + 2 * kQkBytes + 2 * kVBytes + kStageBytes + static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
-
 // Which 32-column groups of a 128 x 128 score tile matter to a warp whose rows are frames
 // w_row0 .. w_row0+31, against keys k0 .. k0+127, under the causal window.
 struct GroupVis {
@@ -164,18 +170,24 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Shared* sh = reinterpret_cast<Shared*>(smem + 2 * kItemBytes);
+  uint8_t* smem_v = smem + 2 * kQkBytes;
+  uint8_t* smem_stage = smem_v + 2 * kVBytes;
+  Shared* sh = reinterpret_cast<Shared*>(smem_stage + kStageBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sh->load_full[i], 1);
+      mbar_init(&sh->qk_full[i], 1);
+      mbar_init(&sh->v_full[i], 1);
+      mbar_init(&sh->qk_done[i], 1);
       mbar_init(&sh->pv_done_a[i], 1);
       mbar_init(&sh->pv_done_b[i], 1);
-      mbar_init(&sh->out_done[i], 8);
     }
+    mbar_init(&sh->out_done_a, 4);
+    mbar_init(&sh->out_done_b[0], 4);
+    mbar_init(&sh->out_done_b[1], 4);
     for (int i = 0; i < kSlots; ++i) {
       mbar_init(&sh->s_full[i], 1);
       mbar_init(&sh->p_full[i], 4);
@@ -206,19 +218,25 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       tma_prefetch_desc(&tmap_q32);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      auto load_item = [&](int n) {
+      auto load_qk = [&](int n) {
         const int item = blockIdx.x + n * gridDim.x;
         const int c = item >> 3, h = item & 7, b = n & 1;
-        uint8_t* base = smem + b * kItemBytes;
-        mbar_arrive_expect_tx(&sh->load_full[b], kItemBytes);
+        uint8_t* base = smem + b * kQkBytes;
+        mbar_arrive_expect_tx(&sh->qk_full[b], kQkBytes);
         // Q0 in four 32-frame boxes, block j of the tile <- frames 96-32j .. 127-32j.
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tma_load_3d(base + j * kSlabBytes, &tmap_q32, &sh->load_full[b], h * kD, (3 - j) * 32, c);
-        tma_load_3d(base + 1 * kTileBytes, &tmap_q, &sh->load_full[b], h * kD, kTile, c);
-        tma_load_3d(base + 2 * kTileBytes, &tmap_k, &sh->load_full[b], h * kD, 0, c);
-        tma_load_3d(base + 3 * kTileBytes, &tmap_k, &sh->load_full[b], h * kD, kTile, c);
-        tma_load_3d(base + 4 * kTileBytes, &tmap_v, &sh->load_full[b], h * kD, 0, c);
-        tma_load_3d(base + 5 * kTileBytes, &tmap_v, &sh->load_full[b], h * kD, kTile, c);
+        for (int j = 0; j < 4; ++j) tma_load_3d(base + j * kSlabBytes, &tmap_q32, &sh->qk_full[b], h * kD, (3 - j) * 32, c);
+        tma_load_3d(base + 1 * kTileBytes, &tmap_q, &sh->qk_full[b], h * kD, kTile, c);
+        tma_load_3d(base + 2 * kTileBytes, &tmap_k, &sh->qk_full[b], h * kD, 0, c);
+        tma_load_3d(base + 3 * kTileBytes, &tmap_k, &sh->qk_full[b], h * kD, kTile, c);
+      };
+      auto load_v = [&](int n) {
+        const int item = blockIdx.x + n * gridDim.x;
+        const int c = item >> 3, h = item & 7, b = n & 1;
+        uint8_t* base = smem_v + b * kVBytes;
+        mbar_arrive_expect_tx(&sh->v_full[b], kVBytes);
+        tma_load_3d(base, &tmap_v, &sh->v_full[b], h * kD, 0, c);
+        tma_load_3d(base + kTileBytes, &tmap_v, &sh->v_full[b], h * kD, kTile, c);
       };
       constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
@@ -232,27 +250,29 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           tc_mma_ts(slot_addr(g_o) + kOCol, slot_addr(g_p) + kPCol + 8u * ks, v + static_cast<uint64_t>(ks) * 128u, idesc_pv,
                     (accumulate || ks != 0) ? 1u : 0u);
       };
-      // nl: next item to load.  ready: items whose load has been seen complete.  gq: next job whose scores
-      // are issued.  pa / pb: next item whose kind-0 / kind-1+2 P V is issued.
-      int nl = 0, ready = 0, gq = 0, pa = 0, pb = 0;
+      // lq / lv: next item whose Q,K / V tiles are requested.  rq / rv: items whose Q,K / V have been seen
+      // to land.  gq: next job whose scores are issued.  pa / pb: next item whose kind-0 / kind-1+2 P V is issued.
+      int lq = 0, lv = 0, rq = 0, rv = 0, gq = 0, pa = 0, pb = 0;
       unsigned long long t_idle = 0;
       uint32_t idle_spins = 0;
       while (pa < n_local || pb < n_local) {
         bool progress = false;
-        if (nl < n_local) {
+        if (lq < n_local &&
+            (lq < 2 || mbar_try_wait(&sh->qk_done[lq & 1], static_cast<uint32_t>((lq - 2) >> 1) & 1u))) {
+          load_qk(lq); ++lq; progress = true;
+        }
+        if (lv < n_local) {
           bool ok = true;
-          if (nl >= 2) {
-            const int b = nl & 1;
-            const uint32_t ph = static_cast<uint32_t>((nl - 2) >> 1) & 1u;
-            ok = mbar_try_wait(&sh->pv_done_a[b], ph) && mbar_try_wait(&sh->pv_done_b[b], ph) &&
-                 mbar_try_wait(&sh->out_done[b], ph);
+          if (lv >= 2) {
+            const uint32_t ph = static_cast<uint32_t>((lv - 2) >> 1) & 1u;
+            ok = mbar_try_wait(&sh->pv_done_a[lv & 1], ph) && mbar_try_wait(&sh->pv_done_b[lv & 1], ph) &&
+                 mbar_try_wait(&sh->out_done_b[lv & 1], ph);
           }
-          if (ok) { load_item(nl); ++nl; progress = true; }
+          if (ok) { load_v(lv); ++lv; progress = true; }
         }
-        if (ready < nl && mbar_try_wait(&sh->load_full[ready & 1], static_cast<uint32_t>(ready >> 1) & 1u)) {
-          ++ready; progress = true;
-        }
-        if (gq < n_jobs && gq / 3 < ready) {
+        if (rq < lq && mbar_try_wait(&sh->qk_full[rq & 1], static_cast<uint32_t>(rq >> 1) & 1u)) { ++rq; progress = true; }
+        if (rv < lv && mbar_try_wait(&sh->v_full[rv & 1], static_cast<uint32_t>(rv >> 1) & 1u)) { ++rv; progress = true; }
+        if (gq < n_jobs && gq / 3 < rq) {
           // The slot's previous job (gq-4) must be out of it: a kind-1 job once its P V has been issued (the
           // tensor core runs in order), the others once their team has read O.
           bool free_slot = true;
@@ -263,29 +283,29 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           if (free_slot) {
             tc_fence_after_sync();
             const int n = gq / 3, kind = gq % 3;
-            const uint8_t* base = smem + (n & 1) * kItemBytes;
+            const uint8_t* base = smem + (n & 1) * kQkBytes;
             const uint64_t qd = umma_desc_sw128(smem_u32(base + (kind == 0 ? 0 : 1) * kTileBytes));
             const uint64_t kd = umma_desc_sw128(smem_u32(base + (kind == 2 ? 3 : 2) * kTileBytes));
 #pragma unroll
             for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(slot_addr(gq), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
             tc_commit(&sh->s_full[gq & 3]);
+            if (kind == 2) tc_commit(&sh->qk_done[n & 1]);     // the item's Q / K tiles may be refilled
             ++gq; progress = true;
           }
         }
-        if (pa < n_local && gq > 3 * pa && mbar_try_wait(&sh->p_full[(3 * pa) & 3], job_phase(3 * pa))) {
+        if (pa < rv && gq > 3 * pa && mbar_try_wait(&sh->p_full[(3 * pa) & 3], job_phase(3 * pa))) {
           tc_fence_after_sync();
-          const uint8_t* base = smem + (pa & 1) * kItemBytes;
-          issue_pv(3 * pa, 3 * pa, base + 4 * kTileBytes, false);
+          issue_pv(3 * pa, 3 * pa, smem_v + (pa & 1) * kVBytes, false);
           tc_commit(&sh->o_full[(3 * pa) & 3]);
           tc_commit(&sh->pv_done_a[pa & 1]);
           ++pa; progress = true;
         }
-        if (pb < n_local && gq > 3 * pb + 2 && mbar_try_wait(&sh->p_full[(3 * pb + 1) & 3], job_phase(3 * pb + 1)) &&
+        if (pb < rv && gq > 3 * pb + 2 && mbar_try_wait(&sh->p_full[(3 * pb + 1) & 3], job_phase(3 * pb + 1)) &&
             mbar_try_wait(&sh->p_full[(3 * pb + 2) & 3], job_phase(3 * pb + 2))) {
           tc_fence_after_sync();
-          const uint8_t* base = smem + (pb & 1) * kItemBytes;
-          issue_pv(3 * pb + 1, 3 * pb + 2, base + 4 * kTileBytes, false);   // P10 V0
-          issue_pv(3 * pb + 2, 3 * pb + 2, base + 5 * kTileBytes, true);    // + P11 V1
+          const uint8_t* vb = smem_v + (pb & 1) * kVBytes;
+          issue_pv(3 * pb + 1, 3 * pb + 2, vb, false);                // P10 V0
+          issue_pv(3 * pb + 2, 3 * pb + 2, vb + kTileBytes, true);    // + P11 V1
           tc_commit(&sh->o_full[(3 * pb + 2) & 3]);
           tc_commit(&sh->o_full[(3 * pb + 1) & 3]);   // nobody waits on it; one completion per slot use
           tc_commit(&sh->pv_done_b[pb & 1]);
@@ -313,12 +333,11 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int r = lg * 32 + lane;             // row of the tile == TMEM lane
     const uint32_t slot = tmem_base + static_cast<uint32_t>(team * kTile) + (static_cast<uint32_t>(lg * 32) << 16);
     for (int g = team; g < n_jobs; g += kSlots) {
-      const int n = g / 3, kind = g % 3, b = n & 1, x = n & 3;
+      const int n = g / 3, kind = g % 3, x = n & 3;
       const uint32_t ph = static_cast<uint32_t>(g >> 2) & 1u;      // this slot's use number
       const uint32_t xph = static_cast<uint32_t>(n >> 2) & 1u;     // this exchange buffer's use number
       const int item = blockIdx.x + n * gridDim.x;
       const int c = item >> 3, h = item & 7;
-      uint8_t* base = smem + b * kItemBytes;
       const int w_row0 = kind == 0 ? (3 - lg) * 32 : kTile + lg * 32;   // first frame held by this warp
       const int i = w_row0 + lane;
       const GroupVis vis(i, w_row0, kind == 2 ? kTile : 0, window);
@@ -327,6 +346,7 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       tc_fence_after_sync();
       float m_raw = tile_row_max(slot, vis);
       if (kind != 0) {
+        // Rows 128-255: exchange the partial maximum with the team of the row's other tile.
         sh->xm[x][r][kind - 1] = m_raw;
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->xm_full[x]);
@@ -353,8 +373,10 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         mbar_wait(&sh->xl_full[x], xph, ctl, status, kErrWaitConsumer);
         l_row += sh->xl[x][r];
       }
-      // Staged in the item's Q tile of these rows, which no MMA reads any more (its scores are complete).
-      uint8_t* slab = base + (kind == 0 ? 0 : kTileBytes) + lg * kSlabBytes;
+      // Rows 0-127 are staged in a slab of their own (the previous item's store out of it must have read
+      // it); rows 128-255 in the item's V1 tile, whose only reader, P11 V1, has completed (o_full).
+      uint8_t* slab = (kind == 0 ? smem_stage : smem_v + (n & 1) * kVBytes + kTileBytes) + lg * kSlabBytes;
+      if (kind == 0 && n >= 1) mbar_wait(&sh->out_done_a, static_cast<uint32_t>(n - 1) & 1u, ctl, status, kErrWaitConsumer);
       stage_output_row<VT>(slot + kOCol, slab, lane, 1.f / l_row);
       tc_fence_before_sync();
       fence_proxy_async_smem();
@@ -366,7 +388,7 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           bulk_commit_group();
           bulk_wait_group_read<0>();
         }
-        mbar_arrive(&sh->out_done[b]);
+        mbar_arrive(kind == 0 ? &sh->out_done_a : &sh->out_done_b[n & 1]);
       }
     }
   }
