@@ -17,7 +17,8 @@
 // kind-2 slot.  The causal diagonal leaves warp w of a kind-0 job 4-w visible 32-key groups (its frames are
 // loaded in permuted order) and warp w of a kind-2 job w+1, which balances the four SM sub-partitions.
 // Outputs are normalised, staged in the item's dead Q tiles and leave through TMA stores.
-// Warps 0-15: softmax teams.  Warp 16: TMA loads + MMA issue (whatever is ready next is issued).
+// Warps 0-15: softmax teams.  Warps 16-19: Q/K loads + score products, P V of kind-0 jobs, P V of kind-1/2
+// jobs, V loads (one thread each).
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -30,7 +31,8 @@ constexpr int kTileBytes = kTile * kD * 2;          // 16 KB
 constexpr int kSlabBytes = 32 * 128;                // 32 rows x 64 x 16 bit
 constexpr int kSlots = 4;
 constexpr int kSoftmaxWarps = 4 * kSlots;
-constexpr int kThreads = (kSoftmaxWarps + 1) * 32;
+constexpr int kIssueWarps = 4;
+constexpr int kThreads = (kSoftmaxWarps + kIssueWarps) * 32;
 constexpr int kTmemCols = 128 * kSlots;
 constexpr uint32_t kPCol = 0, kOCol = 64;           // inside a slot: P over the consumed S, then O
 
@@ -211,13 +213,29 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const int n_local = (n_items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
   const int n_jobs = 3 * n_local;
 
-  if (warp == kSoftmaxWarps) {
-    // ------------------------------------------------------------ TMA loads + MMA issue
-    if (lane == 0) {
+  if (warp >= kSoftmaxWarps) {
+    // ------------------------------------------------------------ four single-purpose issuing warps, one
+    // per SM sub-partition, each a plain in-order loop with blocking waits (lane 0 only):
+    //   warp 16: Q/K loads + score products      warp 17: P V of kind-0 jobs
+    //   warp 18: P V of kind-1 + kind-2 jobs      warp 19: V loads
+    const int role = warp - kSoftmaxWarps;
+    constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
+    constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
+    auto slot_addr = [&](int g) { return tmem_base + static_cast<uint32_t>((g & 3) * kTile); };
+    auto job_phase = [](int g) { return static_cast<uint32_t>(g >> 2) & 1u; };
+    auto item_phase = [](int n) { return static_cast<uint32_t>(n >> 1) & 1u; };
+    // O (+)= P V for one job: A = P from tensor memory (8 columns per 16 keys), B = V (MN-major, 2 KB per 16 keys).
+    auto issue_pv = [&](int g_p, int g_o, const uint8_t* v_tile, bool accumulate) {
+      const uint64_t v = umma_desc_sw128(smem_u32(v_tile));
+#pragma unroll
+      for (int ks = 0; ks < kTile / 16; ++ks)
+        tc_mma_ts(slot_addr(g_o) + kOCol, slot_addr(g_p) + kPCol + 8u * ks, v + static_cast<uint64_t>(ks) * 128u, idesc_pv,
+                  (accumulate || ks != 0) ? 1u : 0u);
+    };
+    if (lane == 0 && role == 0) {
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_q32);
       tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
       auto load_qk = [&](int n) {
         const int item = blockIdx.x + n * gridDim.x;
         const int c = item >> 3, h = item & 7, b = n & 1;
@@ -230,100 +248,71 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         tma_load_3d(base + 2 * kTileBytes, &tmap_k, &sh->qk_full[b], h * kD, 0, c);
         tma_load_3d(base + 3 * kTileBytes, &tmap_k, &sh->qk_full[b], h * kD, kTile, c);
       };
-      auto load_v = [&](int n) {
+      if (n_local > 0) load_qk(0);
+      for (int n = 0; n < n_local; ++n) {
+        if (n + 1 < n_local) {
+          // The other Q/K buffer held item n-1; its tiles are dead once that item's scores exist.
+          if (n >= 1) mbar_wait(&sh->qk_done[(n + 1) & 1], item_phase(n - 1), ctl, status, kErrWaitMma);
+          load_qk(n + 1);
+        }
+        mbar_wait(&sh->qk_full[n & 1], item_phase(n), ctl, status, kErrWaitTma);
+        const uint8_t* base = smem + (n & 1) * kQkBytes;
+        for (int kind = 0; kind < 3; ++kind) {
+          const int g = 3 * n + kind;
+          if (g >= 4) {
+            // The slot's previous job must be out of it: a kind-1 job when the P V product that reads its P
+            // has completed, the others when their team has read O.
+            const int gp = g - 4;
+            if (gp % 3 == 1) mbar_wait(&sh->pv_done_b[(gp / 3) & 1], item_phase(gp / 3), ctl, status, kErrWaitMma);
+            else mbar_wait(&sh->slot_free[gp & 3], job_phase(gp), ctl, status, kErrWaitConsumer);
+          }
+          tc_fence_after_sync();
+          const uint64_t qd = umma_desc_sw128(smem_u32(base + (kind == 0 ? 0 : 1) * kTileBytes));
+          const uint64_t kd = umma_desc_sw128(smem_u32(base + (kind == 2 ? 3 : 2) * kTileBytes));
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(slot_addr(g), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
+          tc_commit(&sh->s_full[g & 3]);
+          if (kind == 2) tc_commit(&sh->qk_done[n & 1]);
+        }
+      }
+    } else if (lane == 0 && role == 1) {
+      for (int n = 0; n < n_local; ++n) {
+        mbar_wait(&sh->v_full[n & 1], item_phase(n), ctl, status, kErrWaitTma);
+        mbar_wait(&sh->p_full[(3 * n) & 3], job_phase(3 * n), ctl, status, kErrWaitConsumer);
+        tc_fence_after_sync();
+        issue_pv(3 * n, 3 * n, smem_v + (n & 1) * kVBytes, false);
+        tc_commit(&sh->o_full[(3 * n) & 3]);
+        tc_commit(&sh->pv_done_a[n & 1]);
+      }
+    } else if (lane == 0 && role == 2) {
+      for (int n = 0; n < n_local; ++n) {
+        mbar_wait(&sh->v_full[n & 1], item_phase(n), ctl, status, kErrWaitTma);
+        mbar_wait(&sh->p_full[(3 * n + 1) & 3], job_phase(3 * n + 1), ctl, status, kErrWaitConsumer);
+        mbar_wait(&sh->p_full[(3 * n + 2) & 3], job_phase(3 * n + 2), ctl, status, kErrWaitConsumer);
+        tc_fence_after_sync();
+        const uint8_t* vb = smem_v + (n & 1) * kVBytes;
+        issue_pv(3 * n + 1, 3 * n + 2, vb, false);                // P10 V0
+        issue_pv(3 * n + 2, 3 * n + 2, vb + kTileBytes, true);    // + P11 V1
+        tc_commit(&sh->o_full[(3 * n + 2) & 3]);
+        tc_commit(&sh->o_full[(3 * n + 1) & 3]);   // nobody waits on it; one completion per slot use
+        tc_commit(&sh->pv_done_b[n & 1]);
+      }
+    } else if (lane == 0 && role == 3) {
+      tma_prefetch_desc(&tmap_v);
+      for (int n = 0; n < n_local; ++n) {
+        const int b = n & 1;
+        if (n >= 2) {
+          // The buffer held item n-2: both of its P V products and the output staged in its V1 tile are done.
+          mbar_wait(&sh->pv_done_a[b], item_phase(n - 2), ctl, status, kErrWaitMma);
+          mbar_wait(&sh->pv_done_b[b], item_phase(n - 2), ctl, status, kErrWaitMma);
+          mbar_wait(&sh->out_done_b[b], item_phase(n - 2), ctl, status, kErrWaitConsumer);
+        }
         const int item = blockIdx.x + n * gridDim.x;
-        const int c = item >> 3, h = item & 7, b = n & 1;
+        const int c = item >> 3, h = item & 7;
         uint8_t* base = smem_v + b * kVBytes;
         mbar_arrive_expect_tx(&sh->v_full[b], kVBytes);
         tma_load_3d(base, &tmap_v, &sh->v_full[b], h * kD, 0, c);
         tma_load_3d(base + kTileBytes, &tmap_v, &sh->v_full[b], h * kD, kTile, c);
-      };
-      constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
-      auto slot_addr = [&](int g) { return tmem_base + static_cast<uint32_t>((g & 3) * kTile); };
-      auto job_phase = [](int g) { return static_cast<uint32_t>(g >> 2) & 1u; };
-      // O (+)= P V for one job: A = P from tensor memory (8 columns per 16 keys), B = V (MN-major, 2 KB per 16 keys).
-      auto issue_pv = [&](int g_p, int g_o, const uint8_t* v_tile, bool accumulate) {
-        const uint64_t v = umma_desc_sw128(smem_u32(v_tile));
-#pragma unroll
-        for (int ks = 0; ks < kTile / 16; ++ks)
-          tc_mma_ts(slot_addr(g_o) + kOCol, slot_addr(g_p) + kPCol + 8u * ks, v + static_cast<uint64_t>(ks) * 128u, idesc_pv,
-                    (accumulate || ks != 0) ? 1u : 0u);
-      };
-      // lq / lv: next item whose Q,K / V tiles are requested.  rq / rv: items whose Q,K / V have been seen
-      // to land.  gq: next job whose scores are issued.  pa / pb: next item whose kind-0 / kind-1+2 P V is issued.
-      int lq = 0, lv = 0, rq = 0, rv = 0, gq = 0, pa = 0, pb = 0;
-      unsigned long long t_idle = 0;
-      uint32_t idle_spins = 0;
-      while (pa < n_local || pb < n_local) {
-        bool progress = false;
-        if (lq < n_local &&
-            (lq < 2 || mbar_try_wait(&sh->qk_done[lq & 1], static_cast<uint32_t>((lq - 2) >> 1) & 1u))) {
-          load_qk(lq); ++lq; progress = true;
-        }
-        if (lv < n_local) {
-          bool ok = true;
-          if (lv >= 2) {
-            const uint32_t ph = static_cast<uint32_t>((lv - 2) >> 1) & 1u;
-            ok = mbar_try_wait(&sh->pv_done_a[lv & 1], ph) && mbar_try_wait(&sh->pv_done_b[lv & 1], ph) &&
-                 mbar_try_wait(&sh->out_done_b[lv & 1], ph);
-          }
-          if (ok) { load_v(lv); ++lv; progress = true; }
-        }
-        if (rq < lq && mbar_try_wait(&sh->qk_full[rq & 1], static_cast<uint32_t>(rq >> 1) & 1u)) { ++rq; progress = true; }
-        if (rv < lv && mbar_try_wait(&sh->v_full[rv & 1], static_cast<uint32_t>(rv >> 1) & 1u)) { ++rv; progress = true; }
-        if (gq < n_jobs && gq / 3 < rq) {
-          // The slot's previous job (gq-4) must be out of it: a kind-1 job once its P V has been issued (the
-          // tensor core runs in order), the others once their team has read O.
-          bool free_slot = true;
-          if (gq >= 4) {
-            const int gp = gq - 4;
-            free_slot = (gp % 3 == 1) ? (pb > gp / 3) : mbar_try_wait(&sh->slot_free[gp & 3], job_phase(gp));
-          }
-          if (free_slot) {
-            tc_fence_after_sync();
-            const int n = gq / 3, kind = gq % 3;
-            const uint8_t* base = smem + (n & 1) * kQkBytes;
-            const uint64_t qd = umma_desc_sw128(smem_u32(base + (kind == 0 ? 0 : 1) * kTileBytes));
-            const uint64_t kd = umma_desc_sw128(smem_u32(base + (kind == 2 ? 3 : 2) * kTileBytes));
-#pragma unroll
-            for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(slot_addr(gq), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
-            tc_commit(&sh->s_full[gq & 3]);
-            if (kind == 2) tc_commit(&sh->qk_done[n & 1]);     // the item's Q / K tiles may be refilled
-            ++gq; progress = true;
-          }
-        }
-        if (pa < rv && gq > 3 * pa && mbar_try_wait(&sh->p_full[(3 * pa) & 3], job_phase(3 * pa))) {
-          tc_fence_after_sync();
-          issue_pv(3 * pa, 3 * pa, smem_v + (pa & 1) * kVBytes, false);
-          tc_commit(&sh->o_full[(3 * pa) & 3]);
-          tc_commit(&sh->pv_done_a[pa & 1]);
-          ++pa; progress = true;
-        }
-        if (pb < rv && gq > 3 * pb + 2 && mbar_try_wait(&sh->p_full[(3 * pb + 1) & 3], job_phase(3 * pb + 1)) &&
-            mbar_try_wait(&sh->p_full[(3 * pb + 2) & 3], job_phase(3 * pb + 2))) {
-          tc_fence_after_sync();
-          const uint8_t* vb = smem_v + (pb & 1) * kVBytes;
-          issue_pv(3 * pb + 1, 3 * pb + 2, vb, false);                // P10 V0
-          issue_pv(3 * pb + 2, 3 * pb + 2, vb + kTileBytes, true);    // + P11 V1
-          tc_commit(&sh->o_full[(3 * pb + 2) & 3]);
-          tc_commit(&sh->o_full[(3 * pb + 1) & 3]);   // nobody waits on it; one completion per slot use
-          tc_commit(&sh->pv_done_b[pb & 1]);
-          ++pb; progress = true;
-        }
-        if (progress) {
-          idle_spins = 0;
-        } else if ((++idle_spins & 255u) == 0u) {
-          // Bounded: give up after kWaitLimitNs without any step becoming possible.
-          if (ctl->abort) break;
-          const unsigned long long now = global_timer_ns();
-          if (idle_spins == 256u) t_idle = now;
-          if (now - t_idle > kWaitLimitNs) {
-            ctl->abort = 1;
-            if (status != nullptr) atomicMax(status, static_cast<int>(kErrWaitConsumer));
-            break;
-          }
-        }
       }
     }
   } else {
