@@ -11,8 +11,9 @@ and load the same state dict.  Two execution modes, no fallback between them:
 ``precision="fp32"`` FP32 verification kernels on CUDA cores, generic in heads / head_dim / window,
                      including chunked calls with a cache.
 
-``o_proj`` (inside the reference call's return value, src/fast_mimi/model.py:1961) runs as a PyTorch
-linear on the kernel's output.
+``o_proj`` (inside the reference call's return value, src/fast_mimi/model.py:1961) runs on the same
+tensor-core GEMM kernel for calls without cache (``ops.out_proj``); for one-frame streaming steps and in
+FP32 mode it is a PyTorch linear on the kernel's FP32 output.
 """
 from __future__ import annotations
 
@@ -77,6 +78,8 @@ class MimiAttentionB200(nn.Module):
         self.o_proj = nn.Linear(num_heads * head_dim, hidden_size, bias=False)
         self._packed: torch.Tensor | None = None
         self._packed_key: tuple | None = None
+        self._wo16: torch.Tensor | None = None
+        self._wo16_key: tuple | None = None
 
     @classmethod
     def from_reference(cls, attn: nn.Module, precision: str = "tc",
@@ -108,6 +111,15 @@ class MimiAttentionB200(nn.Module):
             self._packed_key = key
         return self._packed
 
+    def out_weight(self, dtype: torch.dtype) -> torch.Tensor:
+        """``o_proj.weight`` as a 16-bit tensor, rebuilt when the weight changes."""
+        w = self.o_proj.weight
+        key = (w.data_ptr(), w._version, w.device, dtype)
+        if self._wo16 is None or self._wo16_key != key:
+            self._wo16 = w.detach().to(dtype).contiguous()
+            self._wo16_key = key
+        return self._wo16
+
     def _tc_input_dtype(self, hidden_states: torch.Tensor) -> torch.dtype:
         if self.input_dtype is not None:
             return self.input_dtype
@@ -130,6 +142,11 @@ class MimiAttentionB200(nn.Module):
             core = self._forward_fp32(hidden_states, past_key_values, cos, sin)
         else:
             core = self._forward_tc(hidden_states, past_key_values, cos, sin)
+            if past_key_values is None and self.o_proj.bias is None:
+                # the kernel's 16-bit result feeds the output projection as it is
+                out_dtype = hidden_states.dtype if hidden_states.dtype in ops._VALUE_CODES else torch.float16
+                out = ops.out_proj(core, self.out_weight(core.dtype), out_dtype=out_dtype)
+                return out.to(hidden_states.dtype), None
         return self.o_proj(core.to(self.o_proj.weight.dtype)), None
 
     def _forward_tc(self, hidden_states, cache, cos, sin):

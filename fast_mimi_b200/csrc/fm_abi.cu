@@ -97,6 +97,13 @@ int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos
   return fm_band_attn_prefill_bf16(q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype & 1, status, stream);
 }
 
+int fm_out_proj_f16(const void* attn, const void* w_o, const float* layer_scale, const void* residual, void* y,
+                    long long frames, int value_dtype, int* status, void* stream) {
+  if (frames < 0 || frames > 0x7fffffffLL || value_dtype < 0 || value_dtype > 3) return -1;
+  return fm::launch_out_proj_gemm(attn, w_o, y, layer_scale, residual, static_cast<int>(frames), value_dtype,
+                                  status, static_cast<cudaStream_t>(stream));
+}
+
 int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring_v, float* out,
                              const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
                              int value_dtype, int* status, void* stream) {

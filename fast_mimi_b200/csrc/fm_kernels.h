@@ -23,6 +23,12 @@ struct QkvEpilogueArgs {
   int pos_base;            // added to every position
   int T;                   // frames per clip in this call
   int ring_slots;
+  // Output projection mode (launch_out_proj_gemm): the weight has two 256-wide output tiles instead of
+  // six, results go out through `v` without RoPE as  resid + out_scale[c] * acc  (both optional).
+  int n_tiles;             // 256-wide output tiles of the weight: 6 (q|k|v) or 2 (one 512-wide output)
+  int seg_base;            // segment of output tile 0: 0 (q, k, v in turn) or 2 (plain output)
+  const float* out_scale;  // [512] per-channel factor (the reference's layer scale) or null
+  const uint16_t* resid;   // [M, 512] residual in the output's 16-bit format or null
 };
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
@@ -40,6 +46,10 @@ int launch_band_attn_fp32(const float* q, const float* k, const float* v, float*
                           const long long* strides, cudaStream_t st);
 int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int dtype_flags,
                          int* status, cudaStream_t st);
+// y[M,512] = resid + out_scale * (a[M,512] * w[512,512]^T): the attention output projection with the layer
+// scale and the residual add of the reference's transformer layer folded into the epilogue.
+int launch_out_proj_gemm(const void* a, const void* w, void* y, const float* out_scale, const void* resid, int M,
+                         int dtype_flags, int* status, cudaStream_t st);
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st);
 int launch_band_attn_clip(const void* q, const void* k, const void* v, void* out, int B, int T, int window,

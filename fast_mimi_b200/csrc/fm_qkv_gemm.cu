@@ -125,14 +125,14 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       int stage = 0, gen = -1, cur_tile = -1, preloaded = 0;
       uint32_t phase = 0;
       for (int i = 0; i < u_count; ++i) {
-        const int u = u_begin + i, frame_tile = u / 6, ntile = u % 6;
+        const int u = u_begin + i, frame_tile = u / ep.n_tiles, ntile = u % ep.n_tiles;
         if (frame_tile != cur_tile) {
           ++gen;
           cur_tile = frame_tile;
           for (int kc = preloaded; kc < kKChunks; ++kc) load_a(kc, frame_tile, gen);
           preloaded = 0;
         }
-        const int next_tile = (i + 1 < u_count) ? (u + 1) / 6 : -1;
+        const int next_tile = (i + 1 < u_count) ? (u + 1) / ep.n_tiles : -1;
         const bool roll = next_tile >= 0 && next_tile != frame_tile;   // last unit of this frame tile
         const int n0 = ntile * kBlockN + static_cast<int>(rank) * kHalfN;
         for (int kc = 0; kc < kKChunks; ++kc) {
@@ -155,10 +155,10 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       int stage = 0, gen = -1, cur_tile = -1;
       uint32_t phase = 0;
       for (int i = 0; i < u_count; ++i) {
-        const int u = u_begin + i, frame_tile = u / 6;
+        const int u = u_begin + i, frame_tile = u / ep.n_tiles;
         const bool fresh = frame_tile != cur_tile;        // first unit of a frame tile: wait for its x chunks
         if (fresh) { ++gen; cur_tile = frame_tile; }
-        const int next_tile = (i + 1 < u_count) ? (u + 1) / 6 : -1;
+        const int next_tile = (i + 1 < u_count) ? (u + 1) / ep.n_tiles : -1;
         const bool roll = next_tile >= 0 && next_tile != frame_tile;
         const int buf = i & 1;
         const uint32_t use = static_cast<uint32_t>(i >> 1);
@@ -198,7 +198,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     bool row_ok = false;
     int m0 = 0, cur_tile = -1;
     for (int i = 0; i < u_count; ++i) {
-      const int u = u_begin + i, frame_tile = u / 6, ntile = u % 6;
+      const int u = u_begin + i, frame_tile = u / ep.n_tiles, ntile = u % ep.n_tiles;
       if (frame_tile != cur_tile) {
         cur_tile = frame_tile;
         m0 = (2 * frame_tile + static_cast<int>(rank)) * kBlockM;
@@ -206,7 +206,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
         row_ok = row < M;
         const int clip = row_ok ? static_cast<int>(row / ep.T) : 0;
         const int t = row_ok ? static_cast<int>(row % ep.T) : 0;
-        if (row_ok) {
+        if (row_ok && ep.cos != nullptr) {
           const float4* c4 = reinterpret_cast<const float4*>(ep.cos + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
           const float4* s4 = reinterpret_cast<const float4*>(ep.sin + clip * ep.cos_bstride + static_cast<long long>(t) * 64);
 #pragma unroll
@@ -228,7 +228,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       }
       const int buf = i & 1;
       const uint32_t use = static_cast<uint32_t>(i >> 1);
-      const int seg = ntile >> 1;              // 0 = q, 1 = k, 2 = v
+      const int seg = ep.seg_base + (ntile >> 1);   // 0 = q, 1 = k, 2 = v or the plain output
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
@@ -269,6 +269,36 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
               phi[d / 2] = Pack16<__nv_bfloat16>::pack(o_hi[0], o_hi[1]);
             }
           } else {
+            if (ep.out_scale != nullptr) {
+              // per-channel factor: the same address in every lane, so one broadcast load each
+              const float4* s_lo = reinterpret_cast<const float4*>(ep.out_scale + head * 64 + piece * 16);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float4 a = __ldg(s_lo + j), b = __ldg(s_lo + 8 + j);
+                lo[4 * j] = __float_as_uint(__uint_as_float(lo[4 * j]) * a.x);
+                lo[4 * j + 1] = __float_as_uint(__uint_as_float(lo[4 * j + 1]) * a.y);
+                lo[4 * j + 2] = __float_as_uint(__uint_as_float(lo[4 * j + 2]) * a.z);
+                lo[4 * j + 3] = __float_as_uint(__uint_as_float(lo[4 * j + 3]) * a.w);
+                hi[4 * j] = __float_as_uint(__uint_as_float(hi[4 * j]) * b.x);
+                hi[4 * j + 1] = __float_as_uint(__uint_as_float(hi[4 * j + 1]) * b.y);
+                hi[4 * j + 2] = __float_as_uint(__uint_as_float(hi[4 * j + 2]) * b.z);
+                hi[4 * j + 3] = __float_as_uint(__uint_as_float(hi[4 * j + 3]) * b.w);
+              }
+            }
+            if (ep.resid != nullptr && row_ok) {
+              // this frame's 32 + 32 bytes of the residual: whole sectors, read once
+              const uint4* r_lo = reinterpret_cast<const uint4*>(ep.resid + row * 512 + head * 64 + piece * 16);
+              const uint4 r[4] = {__ldg(r_lo), __ldg(r_lo + 1), __ldg(r_lo + 4), __ldg(r_lo + 5)};
+              const uint32_t* rw = reinterpret_cast<const uint32_t*>(r);
+#pragma unroll
+              for (int d = 0; d < 16; d += 2) {
+                const float2 a = Pack16<VT>::unpack(rw[d / 2]), b = Pack16<VT>::unpack(rw[8 + d / 2]);
+                lo[d] = __float_as_uint(__uint_as_float(lo[d]) + a.x);
+                lo[d + 1] = __float_as_uint(__uint_as_float(lo[d + 1]) + a.y);
+                hi[d] = __float_as_uint(__uint_as_float(hi[d]) + b.x);
+                hi[d + 1] = __float_as_uint(__uint_as_float(hi[d + 1]) + b.y);
+              }
+            }
 #pragma unroll
             for (int d = 0; d < 16; d += 2) {
               plo[d / 2] = Pack16<VT>::pack(__uint_as_float(lo[d]), __uint_as_float(lo[d + 1]));
@@ -327,11 +357,9 @@ static int encode_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, ui
                       CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int dtype_flags,
-                         int* status, cudaStream_t st) {
+static int launch_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep, int M, int dtype_flags,
+                       int* status, cudaStream_t st) {
   using namespace gemm;
-  if (M <= 0) return M == 0 ? 0 : -1;
-  if (ep.T <= 0 || ep.cos == nullptr || ep.sin == nullptr) return -1;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_qkv) | reinterpret_cast<uintptr_t>(ep.q) |
        reinterpret_cast<uintptr_t>(ep.k) | reinterpret_cast<uintptr_t>(ep.v) | reinterpret_cast<uintptr_t>(ep.ring_k) |
        reinterpret_cast<uintptr_t>(ep.ring_v)) & 15u)
@@ -339,7 +367,7 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
   CUtensorMap tmap_x, tmap_w, tmap_q, tmap_k, tmap_v;
   int rc = encode_2d_16bit(&tmap_x, x, static_cast<uint64_t>(M), kHidden, kBlockM, kBlockK);
   if (rc != 0) return rc;
-  rc = encode_2d_16bit(&tmap_w, w_qkv, 1536, kHidden, kHalfN, kBlockK);
+  rc = encode_2d_16bit(&tmap_w, w_qkv, static_cast<uint64_t>(ep.n_tiles) * kBlockN, kHidden, kHalfN, kBlockK);
   if (rc != 0) return rc;
   // Output maps (16-bit elements whatever the float format); a missing output reuses x as a placeholder
   // that the kernel never stores through.
@@ -351,7 +379,7 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
   if (rc != 0) return rc;
   const int m_tiles = (M + kBlockM - 1) / kBlockM;
   const int pair_tiles = (m_tiles + 1) / 2;          // an odd last tile gets a partner that works on padding
-  const int total_units = pair_tiles * 6;            // (pair of frame tiles, 256-wide output tile)
+  const int total_units = pair_tiles * ep.n_tiles;            // (pair of frame tiles, 256-wide output tile)
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -366,6 +394,34 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
   kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_x, tmap_w, tmap_q, tmap_k, tmap_v, ep, M, total_units, idesc,
                                                       status);
   return static_cast<int>(cudaGetLastError());
+}
+
+int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs& ep_in, int M, int dtype_flags,
+                         int* status, cudaStream_t st) {
+  if (M <= 0) return M == 0 ? 0 : -1;
+  if (ep_in.T <= 0 || ep_in.cos == nullptr || ep_in.sin == nullptr) return -1;
+  QkvEpilogueArgs ep = ep_in;
+  ep.n_tiles = 6;
+  ep.seg_base = 0;
+  ep.out_scale = nullptr;
+  ep.resid = nullptr;
+  return launch_gemm(x, w_qkv, ep, M, dtype_flags, status, st);
+}
+
+int launch_out_proj_gemm(const void* a, const void* w, void* y, const float* out_scale, const void* resid, int M,
+                         int dtype_flags, int* status, cudaStream_t st) {
+  if (M <= 0) return M == 0 ? 0 : -1;
+  if (a == nullptr || w == nullptr || y == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(out_scale) | reinterpret_cast<uintptr_t>(resid)) & 15u) return -3;
+  QkvEpilogueArgs ep = {};
+  ep.v = static_cast<uint16_t*>(y);
+  ep.T = M;             // one "clip": positions are not used without RoPE
+  ep.ring_slots = 1;
+  ep.n_tiles = 2;
+  ep.seg_base = 2;
+  ep.out_scale = out_scale;
+  ep.resid = static_cast<const uint16_t*>(resid);
+  return launch_gemm(a, w, ep, M, dtype_flags, status, st);
 }
 
 }  // namespace fm

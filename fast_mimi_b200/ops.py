@@ -109,6 +109,35 @@ def qkv_rope(x, w_qkv, cos, sin, *, value_dtype=torch.float16, out=None, status=
     return q, k, v
 
 
+def out_proj(attn, w_o, *, layer_scale=None, residual=None, out_dtype=None, out=None, status=None):
+    """``residual + layer_scale * (attn @ w_o.T)`` for ``attn [..., 512]`` and ``w_o [512, 512]`` of one 16-bit
+    float type; ``residual`` and the result have ``out_dtype`` (default: ``attn``'s).  ``layer_scale`` is a
+    ``[512]`` float32 vector.  This is ``o_proj`` plus the layer's scale and residual add."""
+    lib = _native.load()
+    _need(attn.dtype in _INPUT_DTYPES, f"attn must be bfloat16 or float16, got {attn.dtype}")
+    _check_frames(attn, "attn", attn.dtype)
+    _need(w_o.is_cuda and w_o.dtype == attn.dtype and w_o.is_contiguous() and tuple(w_o.shape) == (HIDDEN, HIDDEN),
+          f"w_o must be contiguous {attn.dtype} [512, 512]")
+    frames = attn.numel() // HIDDEN
+    out_dtype = out_dtype or (out.dtype if out is not None else attn.dtype)
+    _need(out_dtype in _VALUE_CODES, "the output must be float16 or bfloat16")
+    if out is None:
+        out = torch.empty(attn.shape, dtype=out_dtype, device=attn.device)
+    _check_frames(out, "out", out_dtype, frames)
+    if residual is not None:
+        _check_frames(residual, "residual", out_dtype, frames)
+    if layer_scale is not None:
+        _need(layer_scale.is_cuda and layer_scale.dtype == torch.float32 and layer_scale.is_contiguous()
+              and layer_scale.numel() == HIDDEN, "layer_scale must be contiguous CUDA float32 [512]")
+    flags = _VALUE_CODES[out_dtype] | (2 if attn.dtype == torch.float16 else 0)
+    rc = lib.fm_out_proj_f16(attn.data_ptr(), w_o.data_ptr(),
+                             layer_scale.data_ptr() if layer_scale is not None else None,
+                             residual.data_ptr() if residual is not None else None, out.data_ptr(), frames, flags,
+                             _status_ptr(status, attn), _stream())
+    _native.check(rc, "fm_out_proj_f16")
+    return out
+
+
 def band_attention_prefill(q, k, v, *, window=250, scale=0.125, out=None, status=None):
     """Banded causal attention over rotated ``q, k [B,T,512] bf16`` and ``v [B,T,512]`` (fp16 or bf16)."""
     lib = _native.load()

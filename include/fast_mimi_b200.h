@@ -47,6 +47,17 @@ int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const f
 int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int B, int T,
                               int window, float scale, int value_dtype, int* status, void* stream);
 
+/* y = residual + layer_scale * (attn W_o^T): the output projection that follows the attention core
+ * (src/fast_mimi/model.py:1961) with the layer scale and residual add of the transformer layer
+ * (src/fast_mimi/model.py:2059) folded into the FP32 epilogue.  Same persistent tensor-core kernel as
+ * fm_qkv_rope_bf16, run over the two 256-wide output tiles of W_o.
+ *   attn  [frames, 512], w_o [512, 512]: BF16, or FP16 when value_dtype bit 1 is set
+ *   y, residual [frames, 512]: BF16, or FP16 when value_dtype bit 0 is set; residual may be NULL, and may
+ *           alias y (each element is read by the thread that then writes it)
+ *   layer_scale [512] FP32 or NULL (no scaling) */
+int fm_out_proj_f16(const void* attn, const void* w_o, const float* layer_scale, const void* residual, void* y,
+                    long long frames, int value_dtype, int* status, void* stream);
+
 /* fm_qkv_rope_bf16 followed by fm_band_attn_prefill_bf16 on the same stream: the part of
  * MimiAttention.forward between the input and o_proj (src/fast_mimi/model.py:1896-1951) for a call
  * without cache.  q_ws/k_ws/v_ws are caller-provided workspaces of B*T*512 16-bit elements each. */

@@ -114,6 +114,42 @@ def test_bf16_value_path_is_available_and_close():
     assert O.rel_l2(out.cpu(), ref) < 6e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("frames", [1, 127, 1000, 33 * 250])
+def test_out_proj_with_layer_scale_and_residual_matches_oracle(frames, dtype):
+    """o_proj with the layer scale and residual add in the epilogue; ragged frame counts, both 16-bit types,
+    with and without the optional operands, and in place over the residual."""
+    import fast_mimi_b200 as fm
+    torch.manual_seed(11)
+    a = torch.randn(frames, 512).to(dtype)
+    w = (torch.randn(512, 512) * 0.05).to(dtype)
+    s = torch.rand(512) * 0.5 + 0.01
+    r = torch.randn(frames, 512).to(dtype)
+    tol = 5e-4 if dtype == torch.float16 else 4e-3      # one rounding of the result to the output type
+    st = fm.ops.new_status("cuda")
+    for scale, resid in ((None, None), (s, None), (s, r)):
+        ref = O.out_proj_residual(a.float(), w.float(), scale, None if resid is None else resid.float())
+        got = fm.ops.out_proj(a.cuda(), w.cuda(), layer_scale=None if scale is None else scale.cuda(),
+                              residual=None if resid is None else resid.cuda(), status=st)
+        assert got.dtype == dtype and O.rel_l2(got.float().cpu(), ref) < tol
+    buf = r.cuda().clone()
+    fm.ops.out_proj(a.cuda(), w.cuda(), layer_scale=s.cuda(), residual=buf, out=buf, status=st)
+    assert torch.equal(buf, got)
+    _status_ok(st)
+
+
+def test_out_proj_after_attention_matches_reference_layer():
+    """Projection + attention + o_proj, all three on the tensor-core kernels, vs the reference layer output."""
+    import fast_mimi_b200 as fm
+    g = load_golden("attention_layer_T250.npz")
+    x, wq, wk, wv, wo = regen_attention_layer(int(g["seed"]), int(g["b"]), int(g["t"]))
+    cos, sin = O.rope_tables(torch.arange(x.shape[1]))
+    core = fm.ops.attention_prefill(x.half().cuda(), torch.cat([wq, wk, wv]).half().cuda(), cos.cuda()[None],
+                                    sin.cuda()[None])
+    out = fm.ops.out_proj(core, wo.half().cuda())
+    assert O.rel_l2(out[:, g["rows"]].float().cpu(), g["out"]) < TOL
+
+
 @pytest.mark.parametrize("name", ["attention_layer_T250.npz", "attention_layer_T313.npz"])
 def test_attention_module_matches_reference_layer(name):
     """MimiAttentionB200 (tensor-core path, o_proj included) vs the reference MimiAttention output."""
