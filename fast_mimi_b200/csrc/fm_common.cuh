@@ -247,6 +247,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Arrival that orders nothing: for a consumer whose last use of the guarded resource has already completed
+// in program order (a tensor-memory load followed by tcgen05.wait::ld).  The release form above is a
+// cluster-scope fence over every earlier store of the thread and costs thousands of cycles when shared-memory
+// stores and bulk copies are in flight.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
   uint32_t v;
   asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");

@@ -13,10 +13,12 @@
 // Each CTA's 128x256 FP32 result lands in its own TMEM (two 256-column buffers: the epilogue of one work
 // unit overlaps the MMAs of the next).  The kernel is persistent: 74 pairs walk contiguous ranges of
 // (frame-tile pair, output tile) units, and while the last output tile of a frame tile is being multiplied
-// the x chunks it has finished with are already replaced by the next frame tile's.  Epilogue warps read one frame row per thread (both halves of
-// a RoPE pair sit in the same row), rotate, round, stage 32x64 slabs in swizzled shared memory and write
-// them with TMA stores (full 128-byte lines).  Warps 0-7: epilogue (two per TMEM lane group, two heads
-// each).  Warp 8: TMA producer (+ TMEM allocation).  Warp 9: MMA issuer (leader CTA only).
+// the x chunks it has finished with are already replaced by the next frame tile's.  Epilogue warps read one
+// frame row per thread (both halves of a RoPE pair sit in the same row), hand the accumulator back as soon
+// as their last tensor-memory load has completed, rotate, round, stage 32x64 slabs in swizzled shared memory
+// and write them with TMA stores (full 128-byte lines).  Warps 0-7: epilogue (two per TMEM lane group, two
+// heads each).  Warp 8: W producer (+ TMEM allocation).  Warp 9: MMA issuer (leader CTA only).  Warp 10:
+// x producer.
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -34,7 +36,8 @@ constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB per K chunk
 constexpr int kBBytes = kHalfN * kBlockK * 2;    // 16 KB per stage per CTA
 constexpr int kSlabBytes = 32 * 128;             // one warp's 32 frames x 64 outputs x 16 bit
 constexpr int kEpiWarps = 8;                     // two per TMEM lane group: heads 0,1 and heads 2,3 of a tile
-constexpr int kThreads = (kEpiWarps + 2) * 32;
+constexpr int kHeadsPerWarp = 16 / kEpiWarps;    // a tile has four heads per lane group
+constexpr int kThreads = (kEpiWarps + 3) * 32;   // + W producer, MMA issuer, x producer
 constexpr int kTmemCols = 512;
 constexpr int kSmemBytes = 1024 /*align*/ + kKChunks * kABytes + kStages * kBBytes + kEpiWarps * kSlabBytes + 256;
 
@@ -111,41 +114,39 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
   if (skip) {
     // a previous kernel already reported a timeout through this status word: do nothing
   } else if (warp == kEpiWarps) {
-    // ------------------------------------------------------------ TMA producer (one per CTA)
+    // ------------------------------------------------------------ W producer (one thread per CTA)
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_x);
       tma_prefetch_desc(&tmap_w);
-      auto load_a = [&](int kc, int frame_tile, int gen) {
-        // The chunk's buffer is reused: its MMAs of the previous frame tile must have completed.
-        if (gen > 0) mbar_wait(&bars->a_empty[kc], static_cast<uint32_t>(gen - 1) & 1u, ctl, status, kErrWaitMma);
-        if (leader) mbar_arrive_expect_tx(&bars->a_full[kc], 2 * kABytes);
-        tma_load_2d_pair(smem_a + kc * kABytes, &tmap_x, &bars->a_full[kc], kc * kBlockK,
-                         (2 * frame_tile + static_cast<int>(rank)) * kBlockM);
-      };
-      int stage = 0, gen = -1, cur_tile = -1, preloaded = 0;
+      int stage = 0;
       uint32_t phase = 0;
       for (int i = 0; i < u_count; ++i) {
-        const int u = u_begin + i, frame_tile = u / ep.n_tiles, ntile = u % ep.n_tiles;
-        if (frame_tile != cur_tile) {
-          ++gen;
-          cur_tile = frame_tile;
-          for (int kc = preloaded; kc < kKChunks; ++kc) load_a(kc, frame_tile, gen);
-          preloaded = 0;
-        }
-        const int next_tile = (i + 1 < u_count) ? (u + 1) / ep.n_tiles : -1;
-        const bool roll = next_tile >= 0 && next_tile != frame_tile;   // last unit of this frame tile
+        const int ntile = (u_begin + i) % ep.n_tiles;
         const int n0 = ntile * kBlockN + static_cast<int>(rank) * kHalfN;
         for (int kc = 0; kc < kKChunks; ++kc) {
           mbar_wait(&bars->b_empty[stage], phase ^ 1u, ctl, status, kErrWaitConsumer);
           if (leader) mbar_arrive_expect_tx(&bars->b_full[stage], 2 * kBBytes);
           tma_load_2d_pair(smem_b + stage * kBBytes, &tmap_w, &bars->b_full[stage], kc * kBlockK, n0);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
-          // W stage kc reuses the buffer of stage kc-4, so chunk kc-4's MMAs of this unit are done and
-          // the x chunk can already be replaced by the next frame tile's.
-          if (roll && kc >= kStages) {
-            load_a(kc - kStages, next_tile, gen + 1);
-            preloaded = kc - kStages + 1;
-          }
+        }
+      }
+    }
+  } else if (warp == kEpiWarps + 2) {
+    // ------------------------------------------------------------ x producer (one thread per CTA)
+    // Runs on its own so that waiting for a chunk's last MMA never holds up the W stream: each chunk of
+    // the resident x tile is replaced by the next frame tile's as soon as the tensor core is done with it.
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x);
+      int gen = -1, cur_tile = -1;
+      for (int i = 0; i < u_count; ++i) {
+        const int frame_tile = (u_begin + i) / ep.n_tiles;
+        if (frame_tile == cur_tile) continue;
+        cur_tile = frame_tile;
+        ++gen;
+        for (int kc = 0; kc < kKChunks; ++kc) {
+          if (gen > 0) mbar_wait(&bars->a_empty[kc], static_cast<uint32_t>(gen - 1) & 1u, ctl, status, kErrWaitMma);
+          if (leader) mbar_arrive_expect_tx(&bars->a_full[kc], 2 * kABytes);
+          tma_load_2d_pair(smem_a + kc * kABytes, &tmap_x, &bars->a_full[kc], kc * kBlockK,
+                           (2 * frame_tile + static_cast<int>(rank)) * kBlockM);
         }
       }
     }
@@ -236,7 +237,7 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
       const bool lin_ok = (seg == 0 ? ep.q : (seg == 1 ? ep.k : ep.v)) != nullptr;
       uint16_t* ring = seg == 1 ? ep.ring_k : (seg == 2 ? ep.ring_v : nullptr);
 #pragma unroll 1
-      for (int hh = hsel * 2; hh < hsel * 2 + 2; ++hh) {
+      for (int hh = hsel * kHeadsPerWarp; hh < (hsel + 1) * kHeadsPerWarp; ++hh) {
         const int head = (ntile & 1) * 4 + hh;
         if (lin_ok) {
           // The previous store out of this warp's slab must have finished reading it.
@@ -253,6 +254,13 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
           tmem_ld16(t_row + hh * 64 + piece * 16, lo);
           tmem_ld16(t_row + hh * 64 + 32 + piece * 16, hi);
           tmem_ld_wait();
+          if (hh == (hsel + 1) * kHeadsPerWarp - 1 && piece == 1) {
+            // That was this warp's last read of the accumulator: hand it back before the arithmetic and the
+            // stores.  The loads have completed, so the arrival needs no release ordering.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+          }
           uint32_t plo[8], phi[8];
           if (seg < 2) {
 #pragma unroll
@@ -329,9 +337,6 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
           }
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
     }
     if (lane == 0) bulk_wait_group_read<0>();
   }
