@@ -3,13 +3,15 @@
 Public surface:
   MimiAttentionB200        drop-in for the reference's ``MimiAttention`` (same forward signature)
   native_window_attention  drop-in for the reference's ``_native_window_attention``
+  MimiTransformerLayerB200 drop-in for the reference's ``MimiTransformerLayer`` (whole layer on these kernels)
   MimiKVRing               streaming KV state with ``MimiKVCache``'s bookkeeping interface
   ops                      tensor-level wrappers over the C ABI (include/fast_mimi_b200.h)
 """
 from . import ops
 from .attention import MimiAttentionB200, install, native_window_attention, window_attention_fp32
 from .kv_ring import LinearKVCache, MimiKVRing
+from .layer import MimiTransformerLayerB200, install_layers
 from .sharding import gather_to_host, shard, shard_bounds
 
-__all__ = ["MimiAttentionB200", "MimiKVRing", "LinearKVCache", "install", "native_window_attention",
+__all__ = ["MimiAttentionB200", "MimiTransformerLayerB200", "install_layers", "MimiKVRing", "LinearKVCache", "install", "native_window_attention",
            "window_attention_fp32", "ops", "shard", "shard_bounds", "gather_to_host"]

@@ -104,6 +104,18 @@ int fm_out_proj_f16(const void* attn, const void* w_o, const float* layer_scale,
                                   status, static_cast<cudaStream_t>(stream));
 }
 
+int fm_linear_f16(const void* a, const void* w, const float* scale, const void* residual, void* y, long long rows,
+                  int n_out, int k_in, int in_dtype, int out_dtype, int activation, int* status, void* stream) {
+  if (rows < 0 || rows > 0x7fffffffLL || activation < 0 || activation > 1) return -1;
+  return fm::launch_linear_gemm(a, w, y, scale, residual, static_cast<int>(rows), n_out, k_in, in_dtype, out_dtype,
+                                activation, status, static_cast<cudaStream_t>(stream));
+}
+
+int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const float* bias, float eps, void* y,
+                     int y_dtype, long long rows, void* stream) {
+  return fm::launch_layernorm512(x, x_dtype, weight, bias, eps, y, y_dtype, rows, static_cast<cudaStream_t>(stream));
+}
+
 int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring_v, float* out,
                              const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
                              int value_dtype, int* status, void* stream) {

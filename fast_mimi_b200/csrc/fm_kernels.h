@@ -50,6 +50,13 @@ int launch_qkv_rope_gemm(const void* x, const void* w_qkv, const QkvEpilogueArgs
 // scale and the residual add of the reference's transformer layer folded into the epilogue.
 int launch_out_proj_gemm(const void* a, const void* w, void* y, const float* out_scale, const void* resid, int M,
                          int dtype_flags, int* status, cudaStream_t st);
+// y[M,N] = resid + scale * act(a[M,K] * w[N,K]^T); in_dtype 0 BF16 / 1 FP16; out_dtype 0 BF16 / 1 FP16 / 2 FP32
+// (type of y and resid); gelu 1 = exact GELU.  N a multiple of 256, K a multiple of 64.
+int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale, const void* resid, int M, int N,
+                       int K, int in_dtype, int out_dtype, int gelu, int* status, cudaStream_t st);
+// LayerNorm over 512 channels; x_dtype 0 BF16 / 1 FP16 / 2 FP32, y_dtype 0 BF16 / 1 FP16.
+int launch_layernorm512(const void* x, int x_dtype, const float* weight, const float* bias, float eps, void* y,
+                        int y_dtype, long long rows, cudaStream_t st);
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st);
 int launch_band_attn_clip(const void* q, const void* k, const void* v, void* out, int B, int T, int window,

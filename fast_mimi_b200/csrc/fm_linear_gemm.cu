@@ -1,0 +1,332 @@
+// General bias-free linear layer for sm_100a with a fused epilogue:
+//
+//   y[m, :] = residual[m, :] + scale * act(a[m, :] * W^T)      (M rows x N outputs x K inputs, 16-bit in, FP32 acc)
+//
+// act is the identity or the exact (erf) GELU; scale (per output channel) and residual are optional; y and
+// the residual are BF16, FP16 or FP32.  It serves the linear layers that follow the attention core in the
+// reference's transformer layer: the MLP  fc2(gelu(fc1(.)))  with its layer scale and residual add
+// (src/fast_mimi/model.py:1990-1999, :2060-2061) and, with FP32 residual streams, the output projection
+// (src/fast_mimi/model.py:1961, :2059).
+//
+// Unlike the QKV projection kernel, which keeps its x tile resident because K is only 512, both operands
+// stream here: a stage holds a 128 x 64 slice of a and a 128 x 64 slice of W per CTA (32 KB), six stages deep.
+// Two CTAs form a pair (cluster of 2, tcgen05 cta_group::2): one tcgen05.mma multiplies the pair's 256 rows by
+// 256 weight rows, each CTA contributing half of the weight tile.  Accumulators: two 256-column TMEM buffers
+// per CTA, so the epilogue of one unit overlaps the MMAs of the next.  Persistent: pairs walk contiguous
+// ranges of (row-tile pair, 256-wide output tile) units, row-tile-major, so the a slices of a row tile are
+// re-read from L2 for its later output tiles.  Warps 0-7: epilogue (two per TMEM lane group, two 64-column
+// groups each).  Warp 8: TMA producer (+ TMEM allocation).  Warp 9: MMA issuer (leader CTA only).
+#include <type_traits>
+
+#include "fm_common.cuh"
+#include "fm_kernels.h"
+
+namespace fm {
+
+namespace lin {
+constexpr int kBlockM = 128;           // rows per CTA
+constexpr int kBlockN = 256;           // outputs per unit
+constexpr int kHalfN = kBlockN / 2;    // weight rows loaded by each CTA of the pair
+constexpr int kBlockK = 64;            // one 128-byte swizzle row of 16-bit values
+constexpr int kStages = 6;
+constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
+constexpr int kBBytes = kHalfN * kBlockK * 2;    // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSlabBytes = 32 * 128;             // one warp's staging: 32 rows x 128 bytes
+constexpr int kEpiWarps = 8;
+constexpr int kGroupsPerWarp = 16 / kEpiWarps;   // a unit has four 64-column groups per lane group
+constexpr int kThreads = (kEpiWarps + 2) * 32;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes = 1024 /*align*/ + kStages * kStageBytes + kEpiWarps * kSlabBytes + 256;
+
+struct Barriers {
+  uint64_t full[kStages];      // used in the leader: bytes of both CTAs' a and W slices
+  uint64_t empty[kStages];     // per CTA: stage consumed by the tensor core
+  uint64_t acc_full[2];        // per CTA: accumulator buffer complete
+  uint64_t acc_empty[2];       // used in the leader: 16 epilogue warps (8 per CTA) drained the buffer
+  uint32_t tmem_base;
+  uint32_t skip;
+  CtaCtl ctl;
+};
+static_assert(sizeof(Barriers) <= 256, "barrier block too large");
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+}  // namespace lin
+
+struct LinearArgs {
+  const float* scale;     // [N] or null
+  const void* resid;      // [M, N] in the output's type or null
+  int M, N, K;
+  int gelu;               // 1: exact GELU on the accumulator before scale / residual
+};
+
+// kOut: 0 = BF16, 1 = FP16, 2 = FP32 (type of y and of the residual)
+template <int kOut>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(lin::kThreads, 1)
+linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_y, LinearArgs args, int total_units, uint32_t idesc,
+                   int* status) {
+  using namespace lin;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_stage = smem;                                  // kStages x [a slice | W slice]
+  uint8_t* smem_out = smem_stage + kStages * kStageBytes;      // kEpiWarps x 4 KB
+  Barriers* bars = reinterpret_cast<Barriers*>(smem_out + kEpiWarps * kSlabBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const int n_tiles = args.N / kBlockN;
+  const int k_chunks = args.K / kBlockK;
+  const int pair = static_cast<int>(blockIdx.x >> 1), n_pairs = static_cast<int>(gridDim.x >> 1);
+  const int u_base = total_units / n_pairs, u_extra = total_units % n_pairs;
+  const int u_begin = pair * u_base + (pair < u_extra ? pair : u_extra);
+  const int u_count = u_base + (pair < u_extra ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&bars->full[i], 1);
+      mbar_init(&bars->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->acc_full[i], 1);
+      mbar_init(&bars->acc_empty[i], 2 * kEpiWarps);
+    }
+    bars->ctl.abort = 0;
+    bars->skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1u : 0u;
+    fence_mbar_init();
+  }
+  if (warp == kEpiWarps) {
+    tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  CtaCtl* ctl = &bars->ctl;
+  const bool skip = ld_shared_cluster_u32(map_to_cta(smem_u32(&bars->skip), 0)) != 0;
+
+  if (skip) {
+    // a previous kernel already reported a timeout through this status word: do nothing
+  } else if (warp == kEpiWarps) {
+    // ------------------------------------------------------------ TMA producer (one thread per CTA)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_w);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < u_count; ++i) {
+        const int u = u_begin + i, row_tile = u / n_tiles, ntile = u % n_tiles;
+        const int m0 = (2 * row_tile + static_cast<int>(rank)) * kBlockM;
+        const int n0 = ntile * kBlockN + static_cast<int>(rank) * kHalfN;
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&bars->empty[stage], phase ^ 1u, ctl, status, kErrWaitConsumer);
+          if (leader) mbar_arrive_expect_tx(&bars->full[stage], 2 * kStageBytes);
+          uint8_t* dst = smem_stage + stage * kStageBytes;
+          tma_load_2d_pair(dst, &tmap_a, &bars->full[stage], kc * kBlockK, m0);
+          tma_load_2d_pair(dst + kABytes, &tmap_w, &bars->full[stage], kc * kBlockK, n0);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == kEpiWarps + 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < u_count; ++i) {
+        const int buf = i & 1;
+        const uint32_t use = static_cast<uint32_t>(i >> 1);
+        mbar_wait(&bars->acc_empty[buf], (use & 1u) ^ 1u, ctl, status, kErrWaitConsumer);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBlockN);
+        for (int kc = 0; kc < k_chunks; ++kc) {
+          mbar_wait(&bars->full[stage], phase, ctl, status, kErrWaitTma);
+          tc_fence_after_sync();
+          const uint32_t base = smem_u32(smem_stage + stage * kStageBytes);
+          const uint64_t a_desc = umma_desc_sw128(base);
+          const uint64_t b_desc = umma_desc_sw128(base + kABytes);
+#pragma unroll
+          for (int ks = 0; ks < kBlockK / 16; ++ks) {
+            tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(&bars->empty[stage], 3);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        tc_commit_pair(&bars->acc_full[buf], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 0..7 of both CTAs)
+    const int lg = warp & 3;      // TMEM lane group: rows 32*lg .. 32*lg+31 of the tile
+    const int gsel = warp >> 2;   // which two of the unit's four 64-column groups
+    const uint32_t acc_empty_leader = map_to_cta(smem_u32(&bars->acc_empty[0]), 0);
+    uint8_t* slab = smem_out + warp * kSlabBytes;
+    for (int i = 0; i < u_count; ++i) {
+      const int u = u_begin + i, row_tile = u / n_tiles, ntile = u % n_tiles;
+      const int m0 = (2 * row_tile + static_cast<int>(rank)) * kBlockM;
+      const long long row = static_cast<long long>(m0) + lg * 32 + lane;
+      const bool row_ok = row < args.M;
+      const int buf = i & 1;
+      const uint32_t use = static_cast<uint32_t>(i >> 1);
+      mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
+#pragma unroll 1
+      for (int g = gsel * kGroupsPerWarp; g < (gsel + 1) * kGroupsPerWarp; ++g) {
+        const int col0 = ntile * kBlockN + g * 64;         // first output channel of this group
+        uint32_t raw_lo[32], raw_hi[32];
+        tmem_ld32(t_row + g * 64, raw_lo);
+        tmem_ld32(t_row + g * 64 + 32, raw_hi);
+        tmem_ld_wait();
+        if (g == (gsel + 1) * kGroupsPerWarp - 1) {
+          // Last read of the accumulator by this warp: hand it back before the arithmetic and the stores.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+        }
+        float v[64];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          v[c] = __uint_as_float(raw_lo[c]);
+          v[32 + c] = __uint_as_float(raw_hi[c]);
+        }
+        if (args.gelu) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) v[c] = gelu_erf(v[c]);
+        }
+        if (args.scale != nullptr) {
+          const float4* s4 = reinterpret_cast<const float4*>(args.scale + col0);   // same address in every lane
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 s = __ldg(s4 + j);
+            v[4 * j] *= s.x; v[4 * j + 1] *= s.y; v[4 * j + 2] *= s.z; v[4 * j + 3] *= s.w;
+          }
+        }
+        if (args.resid != nullptr && row_ok) {
+          if constexpr (kOut == 2) {
+            const float4* r4 = reinterpret_cast<const float4*>(static_cast<const float*>(args.resid) + row * args.N + col0);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float4 r = __ldg(r4 + j);
+              v[4 * j] += r.x; v[4 * j + 1] += r.y; v[4 * j + 2] += r.z; v[4 * j + 3] += r.w;
+            }
+          } else {
+            using T16 = typename std::conditional<kOut == 1, __half, __nv_bfloat16>::type;
+            const uint4* r4 = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(args.resid) + row * args.N + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 r = __ldg(r4 + j);
+              const uint32_t w4[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = Pack16<T16>::unpack(w4[e]);
+                v[8 * j + 2 * e] += f.x;
+                v[8 * j + 2 * e + 1] += f.y;
+              }
+            }
+          }
+        }
+        if constexpr (kOut == 2) {
+          // FP32 output: two 32-column halves (128-byte rows) through the same 4 KB slab.
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (lane == 0) bulk_wait_group_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              *reinterpret_cast<float4*>(slab + sw128_offset(lane, c)) =
+                  make_float4(v[h * 32 + 4 * c], v[h * 32 + 4 * c + 1], v[h * 32 + 4 * c + 2], v[h * 32 + 4 * c + 3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_y, slab, col0 + h * 32, m0 + lg * 32);   // rows past M are clipped
+              bulk_commit_group();
+            }
+          }
+        } else {
+          using T16 = typename std::conditional<kOut == 1, __half, __nv_bfloat16>::type;
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            *reinterpret_cast<uint4*>(slab + sw128_offset(lane, c)) =
+                make_uint4(Pack16<T16>::pack(v[8 * c], v[8 * c + 1]), Pack16<T16>::pack(v[8 * c + 2], v[8 * c + 3]),
+                           Pack16<T16>::pack(v[8 * c + 4], v[8 * c + 5]), Pack16<T16>::pack(v[8 * c + 6], v[8 * c + 7]));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_y, slab, col0, m0 + lg * 32);
+            bulk_commit_group();
+          }
+        }
+      }
+    }
+    if (lane == 0) bulk_wait_group_read<0>();
+  }
+
+  // Teardown: neither CTA may leave (or release TMEM) while its partner can still signal it.
+  tc_fence_before_sync();
+  __syncthreads();
+  if (ctl->abort) __nanosleep(20000);   // copies that may still be in flight get time to land
+  cluster_sync_all();
+  if (warp == kEpiWarps) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+static int encode_2d(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes, const void* base, uint64_t rows,
+                     uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * static_cast<uint64_t>(elem_bytes)};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return encode_tiled(map, type, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale, const void* resid, int M, int N,
+                       int K, int in_dtype, int out_dtype, int gelu, int* status, cudaStream_t st) {
+  using namespace lin;
+  if (M < 0 || N <= 0 || K <= 0 || N % kBlockN != 0 || K % kBlockK != 0) return -1;
+  if (in_dtype < 0 || in_dtype > 1 || out_dtype < 0 || out_dtype > 2) return -1;
+  if (M == 0) return 0;
+  if (a == nullptr || w == nullptr || y == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y) |
+       reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(resid)) & 15u)
+    return -3;
+  CUtensorMap tmap_a, tmap_w, tmap_y;
+  const CUtensorMapDataType t16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;   // any 16-bit element type moves alike
+  int rc = encode_2d(&tmap_a, t16, 2, a, static_cast<uint64_t>(M), static_cast<uint64_t>(K), kBlockM, kBlockK);
+  if (rc != 0) return rc;
+  rc = encode_2d(&tmap_w, t16, 2, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kHalfN, kBlockK);
+  if (rc != 0) return rc;
+  if (out_dtype == 2)
+    rc = encode_2d(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), 32, 32);
+  else
+    rc = encode_2d(&tmap_y, t16, 2, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), 32, 64);
+  if (rc != 0) return rc;
+  const int m_tiles = (M + kBlockM - 1) / kBlockM;
+  const int pair_tiles = (m_tiles + 1) / 2;
+  const int total_units = pair_tiles * (N / kBlockN);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;
+  const int n_pairs = total_units < max_pairs ? total_units : max_pairs;
+  const int fmt = in_dtype == 1 ? 0 : 1;   // tcgen05 kind::f16 operand format: 0 = F16, 1 = BF16
+  const uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, fmt, fmt, 0, 0);
+  LinearArgs args = {scale, resid, M, N, K, gelu ? 1 : 0};
+  auto kern = out_dtype == 2 ? linear_gemm_kernel<2> : (out_dtype == 1 ? linear_gemm_kernel<1> : linear_gemm_kernel<0>);
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
+  if (rc != 0) return rc;
+  kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_y, args, total_units, idesc, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fm

@@ -138,6 +138,63 @@ def out_proj(attn, w_o, *, layer_scale=None, residual=None, out_dtype=None, out=
     return out
 
 
+_OUT_CODES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def linear(a, w, *, scale=None, residual=None, activation=None, out_dtype=None, out=None, status=None):
+    """``residual + scale * act(a @ w.T)`` on the tensor core for ``a [..., K]`` and ``w [N, K]`` of one 16-bit
+    float type (K a multiple of 64, N of 256).  ``activation``: ``None`` or ``"gelu"`` (exact erf form);
+    ``scale``: ``[N]`` float32; ``residual`` and the result: ``out_dtype`` (bfloat16, float16 or float32;
+    default ``a``'s type), shaped ``[..., N]``.  Covers the MLP's two linears and the output projection of
+    the reference's transformer layer with their GELU / layer scale / residual add folded in."""
+    lib = _native.load()
+    _need(a.is_cuda and a.dtype in _INPUT_DTYPES and a.is_contiguous(), "a must be a contiguous CUDA bfloat16/float16 tensor")
+    _need(w.is_cuda and w.dtype == a.dtype and w.is_contiguous() and w.dim() == 2 and w.shape[1] == a.shape[-1],
+          f"w must be contiguous {a.dtype} [N, {a.shape[-1]}]")
+    N, K = w.shape
+    _need(K % 64 == 0 and N % 256 == 0, "K must be a multiple of 64 and N a multiple of 256")
+    _need(activation in (None, "gelu"), "activation must be None or 'gelu'")
+    rows = a.numel() // K
+    out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    _need(out_dtype in _OUT_CODES, "the output must be bfloat16, float16 or float32")
+    shape = tuple(a.shape[:-1]) + (N,)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+    for name, t in (("out", out), ("residual", residual)):
+        if t is not None:
+            _need(t.is_cuda and t.dtype == out_dtype and t.is_contiguous() and t.numel() == rows * N,
+                  f"{name} must be a contiguous {out_dtype} tensor of {rows} x {N}")
+    if scale is not None:
+        _need(scale.is_cuda and scale.dtype == torch.float32 and scale.is_contiguous() and scale.numel() == N,
+              f"scale must be contiguous CUDA float32 [{N}]")
+    rc = lib.fm_linear_f16(a.data_ptr(), w.data_ptr(), scale.data_ptr() if scale is not None else None,
+                           residual.data_ptr() if residual is not None else None, out.data_ptr(), rows, N, K,
+                           1 if a.dtype == torch.float16 else 0, _OUT_CODES[out_dtype],
+                           1 if activation == "gelu" else 0, _status_ptr(status, a), _stream())
+    _native.check(rc, "fm_linear_f16")
+    return out
+
+
+def layer_norm(x, weight, bias, *, eps=1e-5, out_dtype=torch.float16, out=None):
+    """LayerNorm over the 512 channels of ``x [..., 512]`` (float32, float16 or bfloat16) in FP32 arithmetic,
+    result rounded once to ``out_dtype`` (float16 or bfloat16) for the projections that consume it."""
+    lib = _native.load()
+    _need(x.dtype in _OUT_CODES, "x must be bfloat16, float16 or float32")
+    _check_frames(x, "x", x.dtype)
+    _need(out_dtype in _VALUE_CODES, "the output must be float16 or bfloat16")
+    for name, t in (("weight", weight), ("bias", bias)):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.numel() == HIDDEN,
+              f"{name} must be contiguous CUDA float32 [512]")
+    rows = x.numel() // HIDDEN
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _check_frames(out, "out", out_dtype, rows)
+    rc = lib.fm_layernorm_f16(x.data_ptr(), _OUT_CODES[x.dtype], weight.data_ptr(), bias.data_ptr(), float(eps),
+                              out.data_ptr(), _VALUE_CODES[out_dtype], rows, _stream())
+    _native.check(rc, "fm_layernorm_f16")
+    return out
+
+
 def band_attention_prefill(q, k, v, *, window=250, scale=0.125, out=None, status=None):
     """Banded causal attention over rotated ``q, k [B,T,512] bf16`` and ``v [B,T,512]`` (fp16 or bf16)."""
     lib = _native.load()

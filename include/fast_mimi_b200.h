@@ -58,6 +58,25 @@ int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void*
 int fm_out_proj_f16(const void* attn, const void* w_o, const float* layer_scale, const void* residual, void* y,
                     long long frames, int value_dtype, int* status, void* stream);
 
+/* General bias-free linear layer with a fused epilogue on the tensor core:
+ *   y = residual + scale * act(a W^T),  act = identity (activation 0) or exact erf GELU (activation 1).
+ * Replaces the MLP's fc1 + GELU and fc2 + layer scale + residual add (src/fast_mimi/model.py:1990-1999,
+ * :2060-2061) and, for FP32 residual streams, o_proj + layer scale + residual (src/fast_mimi/model.py:1961, :2059).
+ *   a [rows, k_in], w [n_out, k_in]: in_dtype 0 = BF16, 1 = FP16.  k_in a multiple of 64, n_out of 256.
+ *   y, residual [rows, n_out]: out_dtype 0 = BF16, 1 = FP16, 2 = FP32; residual may be NULL or alias y.
+ *   scale [n_out] FP32 or NULL. */
+int fm_linear_f16(const void* a, const void* w, const float* scale, const void* residual, void* y,
+                  long long rows, int n_out, int k_in, int in_dtype, int out_dtype, int activation,
+                  int* status, void* stream);
+
+/* LayerNorm over the 512 channels of each frame, FP32 arithmetic, biased variance (nn.LayerNorm as used in
+ * src/fast_mimi/model.py:2021-2024, :2052, :2060), with the result rounded once to the 16-bit type the
+ * projections consume.
+ *   x [rows, 512]: x_dtype 0 = BF16, 1 = FP16, 2 = FP32     y [rows, 512]: y_dtype 0 = BF16, 1 = FP16
+ *   weight, bias [512] FP32 */
+int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const float* bias, float eps, void* y,
+                     int y_dtype, long long rows, void* stream);
+
 /* fm_qkv_rope_bf16 followed by fm_band_attn_prefill_bf16 on the same stream: the part of
  * MimiAttention.forward between the input and o_proj (src/fast_mimi/model.py:1896-1951) for a call
  * without cache.  q_ws/k_ws/v_ws are caller-provided workspaces of B*T*512 16-bit elements each. */
