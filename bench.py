@@ -454,6 +454,9 @@ def run_extra_workload(args) -> None:
     peaks = load_peaks()
     stream = torch.cuda.current_stream()
     g = torch.Generator(device=dev).manual_seed(0)
+    if args.workload == "stack":
+        run_stack(args, dev, peaks, stream, g)
+        return
     if args.workload == "longclip":
         B, T = 16, 2500
         sets = []
@@ -528,6 +531,86 @@ def run_extra_workload(args) -> None:
                                    "algorithmic_bytes": nbytes}}))
 
 
+def run_stack(args, dev, peaks, stream, g) -> None:
+    """Whole transformer layers (LayerNorm, projection + RoPE, banded attention, o_proj, LayerNorm, MLP; seven
+    launches per layer) over config 3's batch: 512 clips x 250 frames x 16 layers, FP32 residual stream,
+    FP16 tensor-core operands.  One JSON line with per-kernel CUDA-event times and rooflines."""
+    from fast_mimi_b200 import ops
+    rows = CLIPS * FRAMES
+    x0 = torch.randn(CLIPS, FRAMES, HIDDEN, device=dev, generator=g)
+    mk = lambda *shape, std: (torch.randn(*shape, device=dev, generator=g) * std).half()
+    layers = [{"qkv": mk(1536, HIDDEN, std=0.04), "o": mk(HIDDEN, HIDDEN, std=0.04), "fc1": mk(2048, HIDDEN, std=0.04),
+               "fc2": mk(HIDDEN, 2048, std=0.02), "ln1w": torch.ones(HIDDEN, device=dev), "ln1b": torch.zeros(HIDDEN, device=dev),
+               "ln2w": torch.ones(HIDDEN, device=dev), "ln2b": torch.zeros(HIDDEN, device=dev),
+               "s1": torch.full((HIDDEN,), 0.01, device=dev), "s2": torch.full((HIDDEN,), 0.01, device=dev)}
+              for _ in range(LAYERS)]
+    pos = torch.arange(FRAMES, device=dev, dtype=torch.float32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, 2, device=dev, dtype=torch.int64).float() / 64))
+    emb = torch.cat((torch.outer(pos, inv),) * 2, -1)
+    cos, sin = emb.cos()[None].contiguous(), emb.sin()[None].contiguous()
+    xa, xb = x0.clone(), torch.empty_like(x0)
+    h = torch.empty(x0.shape, dtype=torch.float16, device=dev)
+    q = torch.empty(x0.shape, dtype=torch.bfloat16, device=dev); k = torch.empty_like(q)
+    v = torch.empty_like(h); core = torch.empty_like(h)
+    gbuf = torch.empty(CLIPS, FRAMES, 2048, dtype=torch.float16, device=dev)
+    status = ops.new_status(dev)
+    names = ["layernorm512 (1)", "qkv_rope_gemm", "band_attn_clip", "linear_gemm o_proj", "layernorm512 (2)",
+             "linear_gemm fc1+gelu", "linear_gemm fc2"]
+
+    def layer(p, x_in, x_mid, x_out, ev=None):
+        def mark():
+            if ev is not None:
+                e = torch.cuda.Event(enable_timing=True); e.record(stream); ev.append(e)
+        mark(); ops.layer_norm(x_in, p["ln1w"], p["ln1b"], out=h)
+        mark(); ops.qkv_rope(h, p["qkv"], cos, sin, out=(q, k, v), status=status)
+        mark(); ops.band_attention_prefill(q, k, v, window=WINDOW, scale=0.125, out=core, status=status)
+        mark(); ops.linear(core, p["o"], scale=p["s1"], residual=x_in, out=x_mid, status=status)
+        mark(); ops.layer_norm(x_mid, p["ln2w"], p["ln2b"], out=h)
+        mark(); ops.linear(h, p["fc1"], activation="gelu", out=gbuf, status=status)
+        mark(); ops.linear(gbuf, p["fc2"], scale=p["s2"], residual=x_mid, out=x_out, status=status)
+        mark()
+
+    def step(evs=None):
+        a, b = xa, xb
+        for p in layers:
+            ev = [] if evs is not None else None
+            layer(p, a, b, a, ev)      # x_mid in b, result back in a
+            if evs is not None:
+                evs.append(ev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    evs: list = []
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index or 0) as clocks:
+        e0.record(stream)
+        for _ in range(args.steps):
+            step(evs)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    if ops.read_status(status) != 0:
+        raise SystemExit("stack: a bounded device wait timed out")
+    ms = e0.elapsed_time(e1) / args.steps
+    per = [statistics.mean(ev[i].elapsed_time(ev[i + 1]) for ev in evs) for i in range(7)]
+    flops = [0, 2 * 512 * 1536, 2048 * pairs(FRAMES) / FRAMES, 2 * 512 * 512, 0, 2 * 512 * 2048, 2 * 512 * 2048]
+    nbytes = [2048 + 1024, 1024 + 3072, 4096, 1024 + 2048 + 2048, 2048 + 1024, 1024 + 4096, 4096 + 2048 + 2048]
+    kernels = []
+    for n, t, f, b in zip(names, per, flops, nbytes):
+        kernels.append({"kernel": n, "ms": t, "share": t / sum(per), "tflops": rows * f / (t / 1e3) / 1e12,
+                        "gbs": rows * b / (t / 1e3) / 1e9, "frac_hbm": rows * b / (t / 1e3) / 1e9 / peaks["hbm_gbs"],
+                        "frac_tensor": rows * f / (t / 1e3) / 1e12 / peaks["bf16_tflops"]})
+    total_flop = rows * sum(flops) * LAYERS
+    print(json.dumps({"metric": "transformer-layer frames/s", "value": rows * LAYERS / (ms / 1e3), "unit": "frames/s",
+                      "n_gpus": 1, "steps": args.steps, "ms_per_step": ms, "dtype": "fp16 operands, fp32 accumulate and residual stream",
+                      "data": "synthetic",
+                      "config": {"workload": "whole transformer layers over BASELINE config 3's batch", "clips": CLIPS,
+                                 "frames": FRAMES, "layers": LAYERS, "launches_per_layer": 7,
+                                 "l2": "per-layer tensors (0.26-0.52 GB each) exceed the 126 MB L2"},
+                      "step_tflops": total_flop / (ms / 1e3) / 1e12, "frac_tensor": total_flop / (ms / 1e3) / 1e12 / peaks["bf16_tflops"],
+                      "gpu_launches": args.steps * LAYERS * 7, "kernels": kernels, "clocks": clocks.summary()}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -537,8 +620,8 @@ def main() -> None:
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
     ap.add_argument("--profile-case", choices=["prefill", "decode"], help="run a small case for ncu and exit")
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream"],
-                    help="prefill = headline (config 3); longclip / stream = configs 4 / 5, one extra JSON line")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "stack"],
+                    help="prefill = headline (config 3); longclip / stream = configs 4 / 5, stack = whole transformer layers; one extra JSON line each")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)

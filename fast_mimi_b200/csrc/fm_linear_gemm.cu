@@ -50,7 +50,26 @@ struct Barriers {
 };
 static_assert(sizeof(Barriers) <= 256, "barrier block too large");
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// Exact-form GELU  0.5 x (1 + erf(x / sqrt 2))  with erf from the rational approximation
+//   erf(z) = 1 - (1 + a1 z + ... + a6 z^6)^-16,  z >= 0,  |error| <= 3e-7   (Abramowitz & Stegun 7.1.28)
+// instead of erff(): 15 issue slots and one reciprocal per value, no branch.  The epilogue is arithmetic-bound
+// with erff() (about 40 slots per value); the approximation error is far below the rounding of the result
+// to 16 bit.  Large |z| overflows the power to +inf, whose reciprocal is 0, i.e. erf = 1.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  float t = fmaf(z, 0.0000430638f, 0.0002765672f);
+  t = fmaf(z, t, 0.0001520143f);
+  t = fmaf(z, t, 0.0092705272f);
+  t = fmaf(z, t, 0.0422820123f);
+  t = fmaf(z, t, 0.0705230784f);
+  t = fmaf(z, t, 1.0f);
+  t *= t; t *= t; t *= t; t *= t;
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  const float e = copysignf(1.0f - r, x);
+  const float hx = 0.5f * x;
+  return fmaf(hx, e, hx);
+}
 }  // namespace lin
 
 struct LinearArgs {
