@@ -177,6 +177,27 @@ def config_dict() -> dict:
 
 
 # --------------------------------------------------------------------------- GPU arm
+def pin_to_gpu_numa_node(gpu_index: int) -> None:
+    """Multi-rank runs: keep this rank's threads (and with them the pinned host buffers it allocates next) on
+    the CPU cores of the NUMA node its GPU hangs off, so that eight ranks' host<->device copies do not all
+    cross the socket interconnect.  Best effort: silently does nothing where sysfs or the call is unavailable."""
+    try:
+        bus = torch.cuda.get_device_properties(gpu_index).pci_bus_id
+        domain = torch.cuda.get_device_properties(gpu_index).pci_domain_id
+        dev_id = torch.cuda.get_device_properties(gpu_index).pci_device_id
+        path = f"/sys/bus/pci/devices/{domain:04x}:{bus:02x}:{dev_id:02x}.0/local_cpulist"
+        cpus: set = set()
+        for part in open(path).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            print(f"rank on GPU {gpu_index}: pinned to {len(allowed)} CPUs of its NUMA node", file=sys.stderr)
+    except Exception as exc:      # noqa: BLE001 - placement is an optimisation only
+        print(f"rank on GPU {gpu_index}: NUMA pinning skipped ({exc})", file=sys.stderr)
+
+
 def run_ours(args) -> None:
     import torch.distributed as dist
     import fast_mimi_b200 as fm
@@ -189,9 +210,15 @@ def run_ours(args) -> None:
         raise SystemExit("bench.py needs a CUDA device: the attention kernels have no CPU fallback")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    real_stdout = None
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"      # keep NCCL's version banner off stdout: one JSON line only
+        # Libraries write banners to file descriptor 1 (NCCL prints its version there).  Everything but the
+        # result line goes to stderr: descriptor 1 is pointed at stderr for the run and the JSON line is written
+        # to a saved copy of the real stdout at the end.
+        sys.stdout.flush()
+        real_stdout = os.dup(1)
+        os.dup2(2, 1)
+        pin_to_gpu_numa_node(local_rank)
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
 
@@ -352,7 +379,11 @@ def run_ours(args) -> None:
             "clocks": clocks.summary(), "cpu_baseline": cpu, "decode": decode, "out_proj": out_proj,
             "step_tflops": (gemm_flop + attn_flop) * LAYERS / (ms_per_step / 1e3) / 1e12,
         }
-        print(json.dumps(line))
+        if real_stdout is None:
+            print(json.dumps(line))
+        else:
+            sys.stdout.flush()
+            os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
