@@ -61,6 +61,8 @@ int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* 
                              float scale, int value_is_fp16, int* status, cudaStream_t st);
 int launch_band_attn_clip(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                           float scale, int value_is_fp16, int* status, cudaStream_t st);
+int launch_band_attn_long(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
+                          float scale, int value_is_fp16, int* status, cudaStream_t st);
 int launch_ring_decode_attn(const void* q, const void* ring_k, const void* ring_v, float* out,
                             const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
                             int value_is_fp16, int* status, cudaStream_t st);

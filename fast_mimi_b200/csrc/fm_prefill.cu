@@ -290,6 +290,9 @@ int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* 
   // Clips that fit two 128-frame tiles take the whole-clip kernel (one CTA per (clip, head) item).
   if (T > kTile && T <= 2 * kTile && B <= (1 << 27))
     return launch_band_attn_clip(q, k, v, out, B, T, window, scale, value_is_fp16, status, st);
+  // Longer clips whose window spans exactly three key tiles per query tile take the run-walking kernel.
+  if (T > 2 * kTile && window > kTile + 1 && window <= 2 * kTile + 1 && B <= (1 << 27))
+    return launch_band_attn_long(q, k, v, out, B, T, window, scale, value_is_fp16, status, st);
   CUtensorMap tq, tk, tv;
   int rc = encode_clip_tile(&tq, q, B, T, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
   if (rc != 0) return rc;

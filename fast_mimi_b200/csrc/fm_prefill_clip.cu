@@ -19,14 +19,15 @@
 // Outputs are normalised, staged in the item's dead Q tiles and leave through TMA stores.
 // Warps 0-15: softmax teams.  Warps 16-19: Q/K loads + score products, P V of kind-0 jobs, P V of kind-1/2
 // jobs, V loads (one thread each).
+#include "fm_attn_tile.cuh"
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
 namespace fm {
 
 namespace clip {
-constexpr int kTile = 128;
-constexpr int kD = 64;
+using attn_tile::kTile;
+using attn_tile::kD;
 constexpr int kTileBytes = kTile * kD * 2;          // 16 KB
 constexpr int kSlabBytes = 32 * 128;                // 32 rows x 64 x 16 bit
 constexpr int kSlots = 4;
@@ -62,103 +63,6 @@ struct Shared {
 constexpr int kQkBytes = 4 * kTileBytes, kVBytes = 2 * kTileBytes, kStageBytes = 4 * kSlabBytes;
 constexpr int kSmemBytes = 1024 + 2 * kQkBytes + 2 * kVBytes + kStageBytes + static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
-// Which 32-column groups of a 128 x 128 score tile matter to a warp whose rows are frames
-// w_row0 .. w_row0+31, against keys k0 .. k0+127, under the causal window.
-struct GroupVis {
-  int vis_lo, vis_hi;   // this thread's visible columns
-  int any_lo, any_hi;   // columns seen by at least one row of the warp
-  int all_lo, all_hi;   // columns seen by every row of the warp
-  __device__ __forceinline__ GroupVis(int i, int w_row0, int k0, int window)
-      : vis_lo(i - window + 1 - k0), vis_hi(i - k0), any_lo(w_row0 - window + 1 - k0), any_hi(w_row0 + 31 - k0),
-        all_lo(w_row0 + 31 - window + 1 - k0), all_hi(w_row0 - k0) {}
-  __device__ __forceinline__ bool skip(int c0) const { return c0 > any_hi || c0 + 31 < any_lo; }
-  __device__ __forceinline__ bool full(int c0) const { return c0 >= all_lo && c0 + 31 <= all_hi; }
-};
-
-// Row maximum of the visible raw scores of a tile (this thread's row).
-__device__ __forceinline__ float tile_row_max(uint32_t s_addr, const GroupVis& g) {
-  float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-  for (int c0 = 0; c0 < kTile; c0 += 32) {
-    if (g.skip(c0)) continue;
-    uint32_t s[32];
-    tmem_ld32(s_addr + c0, s);
-    tmem_ld_wait();
-    if (g.full(c0)) {
-#pragma unroll
-      for (int cc = 0; cc < 32; ++cc) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
-    } else {
-#pragma unroll
-      for (int cc = 0; cc < 32; ++cc)
-        if (c0 + cc >= g.vis_lo && c0 + cc <= g.vis_hi) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
-    }
-  }
-  return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
-}
-
-// exp2(scale * s - m) of this thread's tile row, written over the consumed scores as packed 16-bit pairs
-// (32 keys -> 16 columns, ascending, so a group's P never lands on scores that are still to be read).
-// Returns the row sum.
-template <typename VT>
-__device__ __forceinline__ float tile_row_probs(uint32_t s_addr, uint32_t p_addr, const GroupVis& g, float scale_log2e,
-                                                float m_use) {
-  float l[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-  for (int c0 = 0; c0 < kTile; c0 += 32) {
-    uint32_t pk[16];
-    if (g.skip(c0)) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) pk[j] = 0u;
-    } else {
-      uint32_t s[32];
-      tmem_ld32(s_addr + c0, s);
-      tmem_ld_wait();
-      if (g.full(c0)) {
-#pragma unroll
-        for (int cc = 0; cc < 32; cc += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc]), scale_log2e, -m_use));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc + 1]), scale_log2e, -m_use));
-          pk[cc / 2] = Pack16<VT>::pack(p0, p1);
-          l[(cc >> 1) & 3] += p0 + p1;
-        }
-      } else {
-#pragma unroll
-        for (int cc = 0; cc < 32; cc += 2) {
-          float p[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const bool vis = c0 + cc + e >= g.vis_lo && c0 + cc + e <= g.vis_hi;
-            p[e] = vis ? ex2_approx(fmaf(__uint_as_float(s[cc + e]), scale_log2e, -m_use)) : 0.f;
-          }
-          pk[cc / 2] = Pack16<VT>::pack(p[0], p[1]);
-          l[(cc >> 1) & 3] += p[0] + p[1];
-        }
-      }
-    }
-    tmem_st16(p_addr + (c0 >> 1), pk);
-  }
-  tmem_st_wait();
-  return (l[0] + l[1]) + (l[2] + l[3]);
-}
-
-// This thread's 64 output values from TMEM, normalised, rounded, into row `lane` of a swizzled slab.
-template <typename VT>
-__device__ __forceinline__ void stage_output_row(uint32_t o_addr, uint8_t* slab, int lane, float inv) {
-#pragma unroll
-  for (int d0 = 0; d0 < kD; d0 += 32) {
-    uint32_t o[32];
-    tmem_ld32(o_addr + d0, o);
-    tmem_ld_wait();
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        w[e] = Pack16<VT>::pack(__uint_as_float(o[8 * cc + 2 * e]) * inv, __uint_as_float(o[8 * cc + 2 * e + 1]) * inv);
-      *reinterpret_cast<uint4*>(slab + sw128_offset(lane, d0 / 8 + cc)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-  }
-}
 }  // namespace clip
 
 template <typename VT>
@@ -168,6 +72,7 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                       const __grid_constant__ CUtensorMap tmap_out, int n_items, int T, int window,
                       float scale_log2e, int* status) {
   using namespace clip;
+  using namespace attn_tile;
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
 
   extern __shared__ uint8_t smem_raw[];

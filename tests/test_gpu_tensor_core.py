@@ -103,6 +103,29 @@ def test_other_windows_match_oracle(window):
     assert O.rel_l2(out.cpu(), ref) < TOL
 
 
+@pytest.mark.parametrize("B,T,window", [(1, 257, 250), (2, 384, 250), (1, 385, 130), (1, 640, 257), (3, 1000, 250),
+                                        (20, 520, 250), (40, 300, 200), (1, 2500, 250)])
+def test_long_clips_match_oracle(B, T, window):
+    """Clips longer than two tiles with a window that spans three key tiles: the run-walking kernel.  The cases
+    cover a ragged last tile, both window limits, runs split into segments with halo tiles (few sequences) and
+    several whole-sequence runs per CTA (more sequences than SMs)."""
+    import fast_mimi_b200 as fm
+    gen = torch.Generator().manual_seed(B * 10000 + T)
+    q, k, v = (torch.randn(B, 8, T, 64, generator=gen) / 2 for _ in range(3))
+    ref = O.band_attention_sdpa(q, k, v, window=window, scale=0.125)
+    st = fm.ops.new_status("cuda")
+    frames = lambda t, dt: t.transpose(1, 2).reshape(B, T, 512).to(dt).cuda()
+    out = fm.ops.band_attention_prefill(frames(q, torch.bfloat16), frames(k, torch.bfloat16), frames(v, torch.float16),
+                                        window=window, scale=0.125, status=st)
+    _status_ok(st)
+    got = out.float().cpu().view(B, T, 8, 64).transpose(1, 2)
+    assert torch.isfinite(got).all()
+    assert O.rel_l2(got, ref) < TOL
+    # per-tile check, so that one wrong tile cannot hide in the norm of a long clip
+    for t0 in range(0, T, 128):
+        assert O.rel_l2(got[:, :, t0:t0 + 128], ref[:, :, t0:t0 + 128]) < TOL, t0
+
+
 def test_bf16_value_path_is_available_and_close():
     """value_dtype=bfloat16 (the literal BF16 cache) is supported; its rounding alone costs ~2e-3."""
     import fast_mimi_b200 as fm
