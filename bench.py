@@ -516,7 +516,7 @@ def run_extra_workload(args) -> None:
                                      "clips": B, "frames": T, "window": WINDOW,
                                      "l2": "three input sets in rotation (492 MB)"},
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                       "frac": gbs / peaks["hbm_gbs"], "kernel": "band_attn_prefill_kernel",
+                                       "frac": gbs / peaks["hbm_gbs"], "kernel": "band_attn_long_kernel",
                                        "tensor_tflops": flop / (ms / 1e3) / 1e12}}))
         return
     # stream: the whole of config 5
