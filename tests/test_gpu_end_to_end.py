@@ -43,11 +43,32 @@ class _HFAttentionAdapter(nn.Module):
         return out, None
 
 
+class _HFLayerAdapter(nn.Module):
+    """Same idea one level up: HF's transformer calls layer(hidden_states, attention_mask=..., position_ids=...,
+    ...) and expects a tuple; the drop-in layer takes the reference's positional arguments."""
+
+    def __init__(self, hf_layer):
+        super().__init__()
+        import fast_mimi_b200 as fm
+        self.rotary_emb = hf_layer.self_attn.rotary_emb
+        self.inner = fm.MimiTransformerLayerB200.from_reference(hf_layer)
+
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_values=None,
+                output_attentions=False, use_cache=False, **kwargs):
+        assert past_key_values is None and not output_attentions
+        if position_ids is None:
+            position_ids = torch.arange(hidden_states.shape[1], device=hidden_states.device)[None]
+        cos, sin = self.rotary_emb(hidden_states, position_ids)
+        out, _ = self.inner(hidden_states, None, None, (cos.float(), sin.float()), False)
+        return (out,)
+
+
 def _frame_agreement(a: torch.Tensor, b: torch.Tensor) -> float:
     return float((a == b).all(dim=1).float().mean())
 
 
-def test_rvq_codes_match_reference_with_b200_attention():
+@pytest.mark.parametrize("swap", ["attention", "layers"])
+def test_rvq_codes_match_reference_with_b200_attention(swap):
     from transformers import MimiConfig as HFConfig, MimiModel as HFModel
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
@@ -67,14 +88,18 @@ def test_rvq_codes_match_reference_with_b200_attention():
     audio = audio.cuda()
     with torch.inference_mode():
         stock = model.encode(audio, num_quantizers=8).audio_codes.cpu()
-        for layer_idx, layer in enumerate(model.encoder_transformer.layers):
-            layer.self_attn = _HFAttentionAdapter(layer.self_attn, layer_idx)
+        layers = model.encoder_transformer.layers
+        for layer_idx, layer in enumerate(layers):
+            if swap == "attention":
+                layer.self_attn = _HFAttentionAdapter(layer.self_attn, layer_idx)
+            else:        # LayerNorms, projections, attention, MLP, layer scales and residual adds: all native
+                layers[layer_idx] = _HFLayerAdapter(layer)
         ours = model.encode(audio, num_quantizers=8).audio_codes.cpu()
     golden = g["codes"]
     assert ours.shape == golden.shape == (1, 8, 63)
     stock_vs_ref = _frame_agreement(stock, golden)
     ours_vs_ref = _frame_agreement(ours, golden)
     ours_vs_stock = _frame_agreement(ours, stock)
-    print(f"code-frame agreement: stock GPU vs reference CPU {stock_vs_ref:.4f}, "
+    print(f"[{swap}] code-frame agreement: stock GPU vs reference CPU {stock_vs_ref:.4f}, "
           f"B200 attention vs reference CPU {ours_vs_ref:.4f}, B200 attention vs stock GPU {ours_vs_stock:.4f}")
     assert ours_vs_ref >= 0.995
