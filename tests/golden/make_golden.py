@@ -181,8 +181,9 @@ def transformer_stack_tiny():
          **{"p." + k: v for k, v in state.items()})
 
 
-def end_to_end_codes():
-    """BASELINE config 1: full Mimi forward on CPU (5 s synthetic audio, 8 codebooks) with the weight recipe
+def end_to_end_codes(seconds: int = 5):
+    """BASELINE config 1: full Mimi forward on CPU (5 s synthetic audio, 8 codebooks; also 10 s and 12 s, whose
+    250 and 300 transformer frames reach the whole-clip and the long-clip attention kernels) with the weight recipe
     of tests/conftest.py::fill_state_by_recipe, through the reference MimiModel and its functional runtime;
     HF Transformers' MimiModel (the implementation the reference's own tests compare against) is loaded with
     the same state and must give the same codes, which is what lets it stand in on the GPU box."""
@@ -192,7 +193,7 @@ def end_to_end_codes():
     model = MimiModel(MimiConfig(), attention_backend="sdpa").eval()
     state = fill_state_by_recipe(model.state_dict(), seed=0)
     model.load_state_dict(state)
-    audio = synthetic_audio()
+    audio = synthetic_audio(seconds=seconds)
     with torch.inference_mode():
         codes = model.encode(audio, num_quantizers=8).audio_codes
         functional = PureTorchMimi(model)
@@ -213,7 +214,7 @@ def end_to_end_codes():
              ("encoder_transformer.layers.0.self_attn.q_proj.weight",
               "decoder_transformer.layers.7.self_attn.o_proj.weight",
               "quantizer.semantic_residual_vector_quantizer.layers.0.codebook.embed_sum")}
-    save("e2e_codes_5s.npz", codes=codes, audio_probe=audio[0, 0, :16], enc_tr_in_probe=enc_tr_in[0, ::25, :8],
+    save(f"e2e_codes_{seconds}s.npz", codes=codes, audio_probe=audio[0, 0, :16], enc_tr_in_probe=enc_tr_in[0, ::25, :8],
          enc_tr_out_probe=enc_tr_out[0, ::25, :8], distinct_codes=len(torch.unique(codes)),
          **{"probe." + k: v for k, v in probe.items()})
     print("codes", tuple(codes.shape), "distinct", len(torch.unique(codes)))
@@ -234,4 +235,5 @@ if __name__ == "__main__":
     cached_streams("ring_decode_260.npz", MimiConfig(), 2, [1] * 260, seed=5, std=0.02,
                    keep_steps={0, 1, 2, 127, 248, 249, 250, 251, 259}, bf16_inputs=True)
     transformer_stack_tiny()
-    end_to_end_codes()
+    for seconds in (5, 10, 12):
+        end_to_end_codes(seconds)

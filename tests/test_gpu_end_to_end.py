@@ -1,7 +1,8 @@
 """BASELINE config 1 end to end: full Mimi encode (SEANet -> 8-layer transformer -> downsample -> RVQ,
-8 codebooks) of 5 s of synthetic audio with the B200 attention swapped into every transformer layer;
-RVQ code frames must match the reference's CPU result (tests/golden/e2e_codes_5s.npz) on >= 99.5 % of
-frames (a frame counts only if all 8 codes agree).
+8 codebooks) of 5 s of synthetic audio (and of 10 s and 12 s, which reach the other attention kernels) with the
+B200 attention, or the whole B200 transformer layer, swapped into every encoder-transformer layer; RVQ code
+frames must match the reference's CPU result (tests/golden/e2e_codes_*s.npz) on >= 99.5 % of frames (a frame
+counts only if all 8 codes agree).
 
 The reference checkout is not on the GPU box.  The surrounding model therefore comes from HF Transformers
 (library code; the reference's own tests pin themselves bit-exactly to it, tests/test_parity.py:12-29 of the
@@ -67,12 +68,13 @@ def _frame_agreement(a: torch.Tensor, b: torch.Tensor) -> float:
     return float((a == b).all(dim=1).float().mean())
 
 
+@pytest.mark.parametrize("seconds", [5, 10, 12])     # 125, 250, 300 transformer frames: general, whole-clip, long-clip kernel
 @pytest.mark.parametrize("swap", ["attention", "layers"])
-def test_rvq_codes_match_reference_with_b200_attention(swap):
+def test_rvq_codes_match_reference_with_b200_attention(swap, seconds):
     from transformers import MimiConfig as HFConfig, MimiModel as HFModel
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False
-    g = load_golden("e2e_codes_5s.npz")
+    g = load_golden(f"e2e_codes_{seconds}s.npz")
     cfg = HFConfig()
     cfg._attn_implementation = "sdpa"
     torch.manual_seed(0)
@@ -83,7 +85,7 @@ def test_rvq_codes_match_reference_with_b200_attention(swap):
         assert torch.equal(state[key].flatten()[:4], g["probe." + key]), "weight recipe drifted"
     model.load_state_dict(state, strict=True)
     model = model.cuda()
-    audio = synthetic_audio()
+    audio = synthetic_audio(seconds=seconds)
     assert torch.equal(audio[0, 0, :16], g["audio_probe"])
     audio = audio.cuda()
     with torch.inference_mode():
@@ -96,10 +98,10 @@ def test_rvq_codes_match_reference_with_b200_attention(swap):
                 layers[layer_idx] = _HFLayerAdapter(layer)
         ours = model.encode(audio, num_quantizers=8).audio_codes.cpu()
     golden = g["codes"]
-    assert ours.shape == golden.shape == (1, 8, 63)
+    assert ours.shape == golden.shape == (1, 8, (seconds * 25 + 1) // 2)
     stock_vs_ref = _frame_agreement(stock, golden)
     ours_vs_ref = _frame_agreement(ours, golden)
     ours_vs_stock = _frame_agreement(ours, stock)
-    print(f"[{swap}] code-frame agreement: stock GPU vs reference CPU {stock_vs_ref:.4f}, "
+    print(f"[{swap}, {seconds} s] code-frame agreement: stock GPU vs reference CPU {stock_vs_ref:.4f}, "
           f"B200 attention vs reference CPU {ours_vs_ref:.4f}, B200 attention vs stock GPU {ours_vs_stock:.4f}")
     assert ours_vs_ref >= 0.995
