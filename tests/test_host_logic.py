@@ -121,3 +121,19 @@ def test_two_rank_clip_sharding_and_host_gather_over_gloo(tmp_path):
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert res.returncode == 0, res.stderr[-2000:]
     assert "GLOO_OK" in res.stdout
+
+
+def test_layer_module_keeps_the_reference_parameter_names():
+    """State-dict keys of the drop-in layer are those of the reference's MimiTransformerLayer
+    (src/fast_mimi/model.py:2017-2026 with MimiAttention :1728-1747, MimiMLP :1987-1988, MimiLayerScale :1468)."""
+    import fast_mimi_b200 as fm
+    want = {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+            "mlp.fc1.weight", "mlp.fc2.weight", "input_layernorm.weight", "input_layernorm.bias",
+            "post_attention_layernorm.weight", "post_attention_layernorm.bias", "self_attn_layer_scale.scale",
+            "mlp_layer_scale.scale"}
+    layer = fm.MimiTransformerLayerB200()
+    assert set(layer.state_dict()) == want
+    import pytest
+    import torch
+    with pytest.raises(RuntimeError):        # no CPU path
+        layer(torch.zeros(1, 4, 512), None, None, (torch.zeros(1, 4, 64), torch.zeros(1, 4, 64)), False)
