@@ -12,13 +12,13 @@
 // probabilities P (columns 0-63), which the tensor core reads straight from tensor memory as the A operand
 // of O = P V; O (FP32) lands in columns 64-127 of the slot.  So there is no shared-memory round trip for P,
 // and up to four jobs are in flight: while one team exponentiates, the tensor core works on other slots.
-// Rows 128-255 need both of their tiles: the two teams exchange row maxima (and later row sums) through
-// shared memory, use one common maximum, and the tensor core accumulates both P V products into the
-// kind-2 slot.  The causal diagonal leaves warp w of a kind-0 job 4-w visible 32-key groups (its frames are
+// Rows 128-255 need both of their tiles, but the two jobs do not wait for each other: each uses the maximum
+// of its own tile, its P V product lands in its own slot, and the kind-2 team combines the two partial
+// results at the end:  out = (a1 O1 + a2 O2) / (a1 l1 + a2 l2),  a_k = 2^(m_k - max(m1, m2)).  The causal
+// diagonal leaves warp w of a kind-0 job 4-w visible 32-key groups (its frames are
 // loaded in permuted order) and warp w of a kind-2 job w+1, which balances the four SM sub-partitions.
 // Outputs are normalised, staged in the item's dead Q tiles and leave through TMA stores.
-// Warps 0-15: softmax teams.  Warps 16-19: Q/K loads + score products, P V of kind-0 jobs, P V of kind-1/2
-// jobs, V loads (one thread each).
+// Warps 0-15: softmax teams.  Warps 16-18: Q/K loads + score products, P V products, V loads (one thread each).
 #include "fm_attn_tile.cuh"
 #include "fm_common.cuh"
 #include "fm_kernels.h"
@@ -32,7 +32,7 @@ constexpr int kTileBytes = kTile * kD * 2;          // 16 KB
 constexpr int kSlabBytes = 32 * 128;                // 32 rows x 64 x 16 bit
 constexpr int kSlots = 4;
 constexpr int kSoftmaxWarps = 4 * kSlots;
-constexpr int kIssueWarps = 4;
+constexpr int kIssueWarps = 3;
 constexpr int kThreads = (kSoftmaxWarps + kIssueWarps) * 32;
 constexpr int kTmemCols = 128 * kSlots;
 constexpr uint32_t kPCol = 0, kOCol = 64;           // inside a slot: P over the consumed S, then O
@@ -41,20 +41,17 @@ struct Shared {
   uint64_t qk_full[2];     // Q0 Q1 K0 K1 of the item in this buffer have landed (64 KB)
   uint64_t v_full[2];      // V0 V1 of the item in this buffer have landed (32 KB)
   uint64_t qk_done[2];     // the item's three score products have completed: its Q / K tiles are dead
-  uint64_t pv_done_a[2];   // P V of the item's kind-0 job has completed (reads V0)
-  uint64_t pv_done_b[2];   // P V of the item's kind-1 and kind-2 jobs have completed (read V0, V1)
+  uint64_t pv_done[2];     // the item's three P V products have completed: its V tiles are dead
   uint64_t out_done_a;     // rows 0-127 of an item: the four staged slabs have been read by their TMA stores
   uint64_t out_done_b[2];  // rows 128-255 (staged in the item's V1 tile): likewise, per V buffer
   uint64_t s_full[kSlots];
   uint64_t p_full[kSlots];
   uint64_t o_full[kSlots];
-  uint64_t slot_free[kSlots];   // the team is done with the slot's tensor memory (tested for kinds 0 and 2)
-  uint64_t xm_full[4];     // row maxima of a kind-1 / kind-2 pair are both published (8 warps)
-  uint64_t xl_full[4];     // row sums of the kind-1 job are published (4 warps)
+  uint64_t slot_free[kSlots];   // the slot's O has been read (a kind-1 slot's by the kind-2 team of the item)
+  uint64_t xl_full[4];     // row maximum and sum of the kind-1 job are published (4 warps)
   uint32_t tmem_base;
   CtaCtl ctl;
-  float xm[4][kTile][2];   // partial row maxima of a kind-1 / kind-2 pair, by item % 4
-  float xl[4][kTile];      // row sums of the kind-1 job
+  float xs[4][kTile][2];   // scaled row maximum (-inf: nothing visible) and row sum of the kind-1 job, by item % 4
 };
 // Shared memory: two Q/K buffers (4 tiles each), two V buffers (2 tiles each), four 4 KB output slabs for
 // rows 0-127 (rows 128-255 are staged in the item's V1 tile, which only their own P V product reads).
@@ -89,8 +86,7 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       mbar_init(&sh->qk_full[i], 1);
       mbar_init(&sh->v_full[i], 1);
       mbar_init(&sh->qk_done[i], 1);
-      mbar_init(&sh->pv_done_a[i], 1);
-      mbar_init(&sh->pv_done_b[i], 1);
+      mbar_init(&sh->pv_done[i], 1);
     }
     mbar_init(&sh->out_done_a, 4);
     mbar_init(&sh->out_done_b[0], 4);
@@ -100,7 +96,6 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       mbar_init(&sh->p_full[i], 4);
       mbar_init(&sh->o_full[i], 1);
       mbar_init(&sh->slot_free[i], 4);
-      mbar_init(&sh->xm_full[i], 8);
       mbar_init(&sh->xl_full[i], 4);
     }
     sh->ctl.abort = 0;
@@ -119,10 +114,9 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const int n_jobs = 3 * n_local;
 
   if (warp >= kSoftmaxWarps) {
-    // ------------------------------------------------------------ four single-purpose issuing warps, one
-    // per SM sub-partition, each a plain in-order loop with blocking waits (lane 0 only):
-    //   warp 16: Q/K loads + score products      warp 17: P V of kind-0 jobs
-    //   warp 18: P V of kind-1 + kind-2 jobs      warp 19: V loads
+    // ------------------------------------------------------------ three single-purpose issuing warps,
+    // each a plain in-order loop with blocking waits (lane 0 only):
+    //   warp 16: Q/K loads + score products      warp 17: P V products      warp 18: V loads
     const int role = warp - kSoftmaxWarps;
     constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
     constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
@@ -164,13 +158,8 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const uint8_t* base = smem + (n & 1) * kQkBytes;
         for (int kind = 0; kind < 3; ++kind) {
           const int g = 3 * n + kind;
-          if (g >= 4) {
-            // The slot's previous job must be out of it: a kind-1 job when the P V product that reads its P
-            // has completed, the others when their team has read O.
-            const int gp = g - 4;
-            if (gp % 3 == 1) mbar_wait(&sh->pv_done_b[(gp / 3) & 1], item_phase(gp / 3), ctl, status, kErrWaitMma);
-            else mbar_wait(&sh->slot_free[gp & 3], job_phase(gp), ctl, status, kErrWaitConsumer);
-          }
+          // The slot's previous job must be out of it: its O has been read.
+          if (g >= 4) mbar_wait(&sh->slot_free[g & 3], job_phase(g - 4), ctl, status, kErrWaitConsumer);
           tc_fence_after_sync();
           const uint64_t qd = umma_desc_sw128(smem_u32(base + (kind == 0 ? 0 : 1) * kTileBytes));
           const uint64_t kd = umma_desc_sw128(smem_u32(base + (kind == 2 ? 3 : 2) * kTileBytes));
@@ -181,35 +170,23 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
       }
     } else if (lane == 0 && role == 1) {
-      for (int n = 0; n < n_local; ++n) {
-        mbar_wait(&sh->v_full[n & 1], item_phase(n), ctl, status, kErrWaitTma);
-        mbar_wait(&sh->p_full[(3 * n) & 3], job_phase(3 * n), ctl, status, kErrWaitConsumer);
+      // every job's O = P V goes into its own slot, in job order
+      for (int g = 0; g < n_jobs; ++g) {
+        const int n = g / 3, kind = g % 3;
+        if (kind == 0) mbar_wait(&sh->v_full[n & 1], item_phase(n), ctl, status, kErrWaitTma);
+        mbar_wait(&sh->p_full[g & 3], job_phase(g), ctl, status, kErrWaitConsumer);
         tc_fence_after_sync();
-        issue_pv(3 * n, 3 * n, smem_v + (n & 1) * kVBytes, false);
-        tc_commit(&sh->o_full[(3 * n) & 3]);
-        tc_commit(&sh->pv_done_a[n & 1]);
+        issue_pv(g, g, smem_v + (n & 1) * kVBytes + (kind == 2 ? kTileBytes : 0), false);
+        tc_commit(&sh->o_full[g & 3]);
+        if (kind == 2) tc_commit(&sh->pv_done[n & 1]);
       }
     } else if (lane == 0 && role == 2) {
-      for (int n = 0; n < n_local; ++n) {
-        mbar_wait(&sh->v_full[n & 1], item_phase(n), ctl, status, kErrWaitTma);
-        mbar_wait(&sh->p_full[(3 * n + 1) & 3], job_phase(3 * n + 1), ctl, status, kErrWaitConsumer);
-        mbar_wait(&sh->p_full[(3 * n + 2) & 3], job_phase(3 * n + 2), ctl, status, kErrWaitConsumer);
-        tc_fence_after_sync();
-        const uint8_t* vb = smem_v + (n & 1) * kVBytes;
-        issue_pv(3 * n + 1, 3 * n + 2, vb, false);                // P10 V0
-        issue_pv(3 * n + 2, 3 * n + 2, vb + kTileBytes, true);    // + P11 V1
-        tc_commit(&sh->o_full[(3 * n + 2) & 3]);
-        tc_commit(&sh->o_full[(3 * n + 1) & 3]);   // nobody waits on it; one completion per slot use
-        tc_commit(&sh->pv_done_b[n & 1]);
-      }
-    } else if (lane == 0 && role == 3) {
       tma_prefetch_desc(&tmap_v);
       for (int n = 0; n < n_local; ++n) {
         const int b = n & 1;
         if (n >= 2) {
-          // The buffer held item n-2: both of its P V products and the output staged in its V1 tile are done.
-          mbar_wait(&sh->pv_done_a[b], item_phase(n - 2), ctl, status, kErrWaitMma);
-          mbar_wait(&sh->pv_done_b[b], item_phase(n - 2), ctl, status, kErrWaitMma);
+          // The buffer held item n-2: its P V products and the output staged in its V1 tile are done.
+          mbar_wait(&sh->pv_done[b], item_phase(n - 2), ctl, status, kErrWaitMma);
           mbar_wait(&sh->out_done_b[b], item_phase(n - 2), ctl, status, kErrWaitConsumer);
         }
         const int item = blockIdx.x + n * gridDim.x;
@@ -238,45 +215,49 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
       mbar_wait(&sh->s_full[team], ph, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
-      float m_raw = tile_row_max(slot, vis);
-      if (kind != 0) {
-        // Rows 128-255: exchange the partial maximum with the team of the row's other tile.
-        sh->xm[x][r][kind - 1] = m_raw;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->xm_full[x]);
-        mbar_wait(&sh->xm_full[x], xph, ctl, status, kErrWaitConsumer);
-        m_raw = fmaxf(m_raw, sh->xm[x][r][2 - kind]);
-      }
+      const float m_raw = tile_row_max(slot, vis);
       const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
       float l_row = tile_row_probs<VT>(slot, slot + kPCol, vis, scale_log2e, m_use);
-      if (kind == 1) sh->xl[x][r] = l_row;
+      if (kind == 1) {
+        sh->xs[x][r][0] = (m_raw == -INFINITY) ? -INFINITY : m_use;
+        sh->xs[x][r][1] = l_row;
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&sh->p_full[team]);
-        if (kind == 1) {
-          mbar_arrive(&sh->xl_full[x]);
-          mbar_arrive(&sh->slot_free[team]);   // keeps the barrier's phase in step with the slot's use count
-        }
+        if (kind == 1) mbar_arrive(&sh->xl_full[x]);
       }
-      if (kind == 1) continue;                 // the kind-2 team finishes rows 128-255
+      if (kind == 1) continue;                 // its O stays in the slot until the kind-2 team has combined it
 
       mbar_wait(&sh->o_full[team], ph, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
+      // Weights of the two partial results of rows 128-255 (kind 0: a single one).  The P V product of the
+      // kind-1 job was issued before this job's, so it has completed as well.
+      float c_own = 1.f / l_row, c_other = 0.f;
+      const uint32_t other = tmem_base + static_cast<uint32_t>(((g - 1) & 3) * kTile) + (static_cast<uint32_t>(lg * 32) << 16);
       if (kind == 2) {
         mbar_wait(&sh->xl_full[x], xph, ctl, status, kErrWaitConsumer);
-        l_row += sh->xl[x][r];
+        const float m1 = sh->xs[x][r][0], l1 = sh->xs[x][r][1];
+        const float m = fmaxf(m_use, m1);
+        const float a2 = ex2_approx(m_use - m);
+        const float a1 = (m1 == -INFINITY) ? 0.f : ex2_approx(m1 - m);
+        const float inv = 1.f / (a1 * l1 + a2 * l_row);
+        c_own = a2 * inv;
+        c_other = a1 * inv;
       }
       // Rows 0-127 are staged in a slab of their own (the previous item's store out of it must have read
       // it); rows 128-255 in the item's V1 tile, whose only reader, P11 V1, has completed (o_full).
       uint8_t* slab = (kind == 0 ? smem_stage : smem_v + (n & 1) * kVBytes + kTileBytes) + lg * kSlabBytes;
       if (kind == 0 && n >= 1) mbar_wait(&sh->out_done_a, static_cast<uint32_t>(n - 1) & 1u, ctl, status, kErrWaitConsumer);
-      stage_output_row<VT>(slot + kOCol, slab, lane, 1.f / l_row);
+      if (kind == 2) stage_output_row2<VT>(slot + kOCol, other + kOCol, slab, lane, c_own, c_other);
+      else stage_output_row<VT>(slot + kOCol, slab, lane, c_own);
       tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&sh->slot_free[team]);
+        if (kind == 2) mbar_arrive(&sh->slot_free[(g - 1) & 3]);
         if (w_row0 < T) {                      // frames past T are clipped by the map
           tma_store_3d(&tmap_out, slab, h * kD, w_row0, c);
           bulk_commit_group();
