@@ -39,7 +39,7 @@ CLIPS, FRAMES, LAYERS, HIDDEN, WINDOW = 512, 250, 16, 512, 250
 QKV_FLOP_PER_FRAME = 2 * 512 * 1536
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
 # profiles/, taken on a 256-clip case and scaled to this workload's 512 clips (traffic grows with frames).
-NCU_TRAFFIC_BYTES = {"qkv_rope_gemm_kernel": 2 * 220.7e6, "band_attn_prefill_kernel": 2 * 236.4e6}
+NCU_TRAFFIC_BYTES = {"qkv_rope_gemm_kernel": 2 * 217.5e6, "band_attn_prefill_kernel": 2 * 237.0e6}
 
 
 def pairs(t: int, window: int = WINDOW) -> int:
