@@ -3,15 +3,18 @@
 Public surface:
   MimiAttentionB200        drop-in for the reference's ``MimiAttention`` (same forward signature)
   native_window_attention  drop-in for the reference's ``_native_window_attention``
+  window_attention_nlc     drop-in for the reference's long-sequence ``_window_attention_nlc`` ([B, T, 512] result)
+  rope_tables              the FP32 cos / sin tables of the reference's ``MimiRotaryEmbedding``
   MimiTransformerLayerB200 drop-in for the reference's ``MimiTransformerLayer`` (whole layer on these kernels)
   MimiKVRing               streaming KV state with ``MimiKVCache``'s bookkeeping interface
   ops                      tensor-level wrappers over the C ABI (include/fast_mimi_b200.h)
 """
 from . import ops
-from .attention import MimiAttentionB200, install, native_window_attention, window_attention_fp32
+from .attention import (MimiAttentionB200, install, native_window_attention, rope_tables, window_attention_fp32,
+                        window_attention_nlc)
 from .kv_ring import LinearKVCache, MimiKVRing
 from .layer import MimiTransformerLayerB200, install_layers
 from .sharding import gather_to_host, shard, shard_bounds
 
 __all__ = ["MimiAttentionB200", "MimiTransformerLayerB200", "install_layers", "MimiKVRing", "LinearKVCache", "install", "native_window_attention",
-           "window_attention_fp32", "ops", "shard", "shard_bounds", "gather_to_host"]
+           "window_attention_fp32", "window_attention_nlc", "rope_tables", "ops", "shard", "shard_bounds", "gather_to_host"]

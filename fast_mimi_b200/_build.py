@@ -60,7 +60,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         subprocess.run(cmd, check=True)
         objs.append(obj)
     tmp = LIB_PATH + ".tmp"
-    subprocess.run([nvcc, "-shared", "-o", tmp, *objs], check=True)
+    # the link step names the same architecture, so nvcc does not fall back to (and warn about) its default one
+    subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs], check=True)
     os.replace(tmp, LIB_PATH)
     return LIB_PATH
 

@@ -51,6 +51,41 @@ def window_attention_fp32(query, key, value, *, scale, window, q_offset=0, k_off
                                    q_offset=q_offset, k_offset=k_offset)
 
 
+def window_attention_nlc(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, scale: float = 0.125,
+                         window: int = 250, value_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Banded attention that returns the frame-major ``[B, T, 512]`` tensor ``o_proj`` consumes, as the
+    reference's long-sequence helper ``_window_attention_nlc(query, key, value)`` does
+    (src/fast_mimi/_optimized_runtime.py:1718-1846): rotated ``query, key`` and ``value`` shaped ``[B, 8, T, 64]``
+    in, no transpose of the result (it is the kernels' native layout), result in ``query.dtype``.  Where the
+    reference re-batches 64-query blocks against 320 keys, the long-clip kernel walks 128-query tiles over
+    rings of K / V tiles and reads every byte once."""
+    ops._need(query.dim() == 4 and query.shape[1] == ops.HEADS and query.shape[3] == ops.HEAD_DIM,
+              "query must be [B, 8, T, 64]")
+    ops._need(key.shape == query.shape and value.shape == query.shape, "key/value must match query")
+    B, H, T, D = query.shape
+
+    def frames(t, dtype):
+        return t.transpose(1, 2).to(dtype).contiguous().view(B, T, H * D)
+
+    out = ops.band_attention_prefill(frames(query, torch.bfloat16), frames(key, torch.bfloat16),
+                                     frames(value, value_dtype), window=window, scale=scale)
+    return out.to(query.dtype)
+
+
+def rope_tables(position_ids: torch.Tensor, *, head_dim: int = 64, theta: float = 10000.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """The ``position_embeddings`` pair the attention entry points take: FP32 ``cos, sin`` shaped
+    ``[batch, frames, head_dim]`` for absolute ``position_ids [batch, frames]``, computed like the reference's
+    ``MimiRotaryEmbedding.forward`` (src/fast_mimi/model.py:1499-1535): ``inv_freq = theta^(-2j/head_dim)`` in
+    FP32, frequencies by an FP32 product with autocast off, both halves of the table equal."""
+    ops._need(position_ids.dim() == 2, "position_ids must be [batch, frames]")
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    inv_freq = inv_freq.to(position_ids.device)
+    with torch.autocast(device_type=position_ids.device.type, enabled=False):
+        freqs = position_ids.float()[:, :, None] * inv_freq[None, None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        return emb.cos().contiguous(), emb.sin().contiguous()
+
+
 class MimiAttentionB200(nn.Module):
     def __init__(self, hidden_size: int = 512, num_heads: int = 8, head_dim: int = 64, sliding_window: int = 250,
                  layer_idx: int = 0, precision: str = "tc", value_dtype: torch.dtype = torch.float16,

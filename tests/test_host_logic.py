@@ -137,3 +137,18 @@ def test_layer_module_keeps_the_reference_parameter_names():
     import torch
     with pytest.raises(RuntimeError):        # no CPU path
         layer(torch.zeros(1, 4, 512), None, None, (torch.zeros(1, 4, 64), torch.zeros(1, 4, 64)), False)
+
+
+def test_rope_tables_match_the_oracle():
+    """fast_mimi_b200.rope_tables against the oracle's restatement (which the fixtures pin to the tables of the
+    reference's MimiRotaryEmbedding), including non-zero and per-clip position offsets."""
+    import torch
+    import fast_mimi_b200 as fm
+    from oracle import mimi_attention_oracle as O
+    pos = torch.stack([torch.arange(0, 40), torch.arange(1000, 1040)])
+    cos, sin = fm.rope_tables(pos)
+    assert cos.shape == (2, 40, 64) and cos.dtype == torch.float32
+    for b in range(2):
+        oc, os_ = O.rope_tables(pos[b])
+        assert torch.equal(cos[b], oc) and torch.equal(sin[b], os_)
+    assert torch.equal(cos[..., :32], cos[..., 32:])

@@ -107,3 +107,18 @@ def test_tiny_stack_prefill_and_chunked_match_reference():
     cache = O.KVCacheOracle(window=8)
     outs = [run(g["x"][:, a:b], cache) for a, b in ((0, 5), (5, 6), (6, 13), (13, 14), (14, 21))]
     assert (torch.cat(outs, 1) - g["chunked"]).abs().max() < TOL
+
+
+def test_layer_block_restatements_equal_the_library_calls_the_reference_makes():
+    """layer_norm / mlp / out_proj_residual are explicit formulas; the reference calls nn.LayerNorm, nn.Linear
+    and F.gelu (src/fast_mimi/model.py:1999, 2021-2024, 2052-2061).  The golden two-layer stack pins them through
+    transformer_layer; this pins each on its own at Mimi's widths."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(5, 7, 512, generator=g) * 2 + 0.3
+    w, b = torch.rand(512, generator=g) + 0.5, torch.randn(512, generator=g) * 0.1
+    assert (O.layer_norm(x, w, b, 1e-5) - F.layer_norm(x, (512,), w, b, 1e-5)).abs().max() < 2e-6
+    fc1, fc2 = torch.randn(2048, 512, generator=g) * 0.04, torch.randn(512, 2048, generator=g) * 0.02
+    assert torch.equal(O.mlp(x, fc1, fc2), F.linear(F.gelu(F.linear(x, fc1)), fc2))
+    wo, s = torch.randn(512, 512, generator=g) * 0.04, torch.rand(512, generator=g)
+    assert torch.equal(O.out_proj_residual(x, wo, s, x), x + F.linear(x, wo) * s)
