@@ -58,3 +58,55 @@ def test_decode_step_equals_prefill_last_row():
                                  ring.ring_v[0], t)
         if t in (0, 1, 249, 250, 299):
             assert O.rel_l2(out.cpu(), pre[:, t].float().cpu()) < 2e-3, t
+
+
+def test_prefill_and_decode_replay_inside_a_cuda_graph():
+    """The entry points launch on the caller's stream without allocating, synchronising or reading back, so a
+    captured graph replays them: prefill on new input, and streaming steps whose positions live in device
+    memory (the reference captures its whole transformer the same way,
+    src/fast_mimi/_optimized_runtime.py:1221-1241)."""
+    import fast_mimi_b200 as fm
+    from oracle import mimi_attention_oracle as O
+    ops = fm.ops
+    torch.manual_seed(9)
+    dev = "cuda"
+    B, T, S = 6, 250, 32
+    w = (torch.randn(1536, 512, device=dev) * 0.02).bfloat16()
+    cos, sin = (t.to(dev) for t in O.rope_tables(torch.arange(T)))
+    x = torch.randn(B, T, 512, device=dev).bfloat16()
+    ws = tuple(torch.empty(B, T, 512, dtype=dt, device=dev) for dt in (torch.bfloat16, torch.bfloat16, torch.float16))
+    out = torch.empty(B, T, 512, dtype=torch.float16, device=dev)
+    st = ops.new_status(dev)
+    ops.attention_prefill(x, w, cos[None], sin[None], workspace=ws, out=out, status=st)     # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.attention_prefill(x, w, cos[None], sin[None], workspace=ws, out=out, status=st)
+    x2 = torch.randn(B, T, 512, device=dev).bfloat16()
+    want = ops.attention_prefill(x2, w, cos[None], sin[None])
+    x.copy_(x2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+
+    # streaming: one captured step, replayed with the position, the RoPE row and the input updated in place
+    ring_g, ring_e = fm.MimiKVRing(1, S, 250, device=dev), fm.MimiKVRing(1, S, 250, device=dev)
+    xs = torch.zeros(S, 512, dtype=torch.bfloat16, device=dev)
+    pos = torch.zeros(S, dtype=torch.int32, device=dev)
+    c1, s1 = torch.zeros(1, 1, 64, device=dev), torch.zeros(1, 1, 64, device=dev)
+    qw = torch.empty_like(xs)
+    o = torch.empty(S, 512, device=dev)
+    scratch = fm.MimiKVRing(1, S, 250, device=dev)
+    ops.decode_step(xs, w, c1, s1, scratch.ring_k[0], scratch.ring_v[0], 0, stream_pos=pos, q_workspace=qw, out=o, status=st)
+    torch.cuda.synchronize()
+    step = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(step):
+        ops.decode_step(xs, w, c1, s1, ring_g.ring_k[0], ring_g.ring_v[0], 0, stream_pos=pos, q_workspace=qw, out=o, status=st)
+    for t in range(6):
+        frame = torch.randn(S, 512, device=dev).bfloat16()
+        xs.copy_(frame); pos.fill_(t); c1.copy_(cos[t].view(1, 1, 64)); s1.copy_(sin[t].view(1, 1, 64))
+        step.replay()
+        eager = ops.decode_step(frame, w, cos[None, t:t + 1], sin[None, t:t + 1], ring_e.ring_k[0], ring_e.ring_v[0], t)
+        torch.cuda.synchronize()
+        assert torch.equal(o, eager), t
+    assert ops.read_status(st) == 0

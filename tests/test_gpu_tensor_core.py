@@ -126,6 +126,19 @@ def test_long_clips_match_oracle(B, T, window):
         assert O.rel_l2(got[:, :, t0:t0 + 128], ref[:, :, t0:t0 + 128]) < TOL, t0
 
 
+def test_window_attention_nlc_returns_frame_major_layout():
+    """The long-sequence helper of the reference returns [1, T, 512]; ours is the same numbers as
+    native_window_attention without the transpose back to [B, H, T, D]."""
+    import fast_mimi_b200 as fm
+    gen = torch.Generator().manual_seed(77)
+    q, k, v = (torch.randn(1, 8, 1000, 64, generator=gen) / 2 for _ in range(3))
+    nlc = fm.window_attention_nlc(q.cuda(), k.cuda(), v.cuda())
+    bhtd = fm.native_window_attention(q.cuda(), k.cuda(), v.cuda(), scale=0.125, window=250)
+    assert nlc.shape == (1, 1000, 512) and nlc.dtype == torch.float32
+    assert torch.equal(nlc, bhtd.transpose(1, 2).reshape(1, 1000, 512))
+    assert O.rel_l2(nlc.cpu().view(1, 1000, 8, 64).transpose(1, 2), O.band_attention_sdpa(q, k, v, scale=0.125)) < TOL
+
+
 def test_bf16_value_path_is_available_and_close():
     """value_dtype=bfloat16 (the literal BF16 cache) is supported; its rounding alone costs ~2e-3."""
     import fast_mimi_b200 as fm
