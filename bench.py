@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 3, "batched prefill"): per GPU 512 clips of 250 frames (10 s at 25 Hz)
+Workload (benchmark config 3, "batched prefill"): per GPU 512 clips of 250 frames (10 s at 25 Hz)
 through the attention path of 16 transformer layers (8 encoder + 8 decoder): QKV projection + RoPE +
 banded causal attention (window 250), BF16 inputs, FP32 accumulate.  One step = one pass of the 16
 layers over the batch.  Metric: attention frames/s = clips * frames * layers / time, summed over GPUs.
@@ -14,7 +14,7 @@ host->device copy of the batch from pinned memory and the device->host copy of t
 every step.  `roofline` describes the kernel with the largest share of the step, timed with CUDA events
 on the launching stream inside the timed region.  `cpu_baseline` is the CPU oracle (a PyTorch FP32
 restatement of the reference's attention, all host threads) on a bounded sample of the same workload.
-`decode` adds the streaming single-frame step (BASELINE config 5) on a full 250-slot ring.
+`decode` adds the streaming single-frame step (benchmark config 5) on a full 250-slot ring.
 
 `--impl reference` times that CPU restatement instead (the reference is PyTorch code whose CPU path is
 exactly these library calls; the reference checkout itself does not travel to the GPU box).
@@ -171,7 +171,7 @@ def run_reference(args) -> None:
 
 
 def config_dict() -> dict:
-    return {"workload": "batched prefill (BASELINE config 3): QKV projection + RoPE + banded causal attention, "
+    return {"workload": "batched prefill (benchmark config 3): QKV projection + RoPE + banded causal attention, "
                         "16 layers", "clips_per_gpu": CLIPS, "frames": FRAMES, "layers": LAYERS, "window": WINDOW,
             "heads": 8, "head_dim": 64, "l2": "inputs larger than L2: each layer streams 655 MB (x, q, k, v, out)"}
 
@@ -314,7 +314,7 @@ def run_ours(args) -> None:
     barrier()
     ms_e2e = s2.elapsed_time(t2)
 
-    # ---- streaming decode (BASELINE config 5) on a full ring ----------------------------------
+    # ---- streaming decode (benchmark config 5) on a full ring ----------------------------------
     decode = None
     if not args.no_decode:
         decode = bench_decode(dev, stream, peaks, world, rank)
@@ -438,7 +438,7 @@ def bench_decode(dev, stream, peaks, world, rank, streams: int = 4096, layers: i
     gbs = bytes_layer / (layer_ms / 1e3) / 1e9
     del ring
     torch.cuda.empty_cache()
-    return {"workload": "streaming decode (BASELINE config 5), full 250-slot ring", "streams_per_gpu": streams,
+    return {"workload": "streaming decode (benchmark config 5), full 250-slot ring", "streams_per_gpu": streams,
             "layers": layers, "steps": steps, "ms_per_step": ms_step,
             "value": streams * layers * world / (ms_step / 1e3), "unit": "frames/s",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -449,7 +449,9 @@ def bench_decode(dev, stream, peaks, world, rank, streams: int = 4096, layers: i
 def profile_case(which: str) -> None:
     """Small cases for `ncu --set full` captures (inputs above the 126 MB L2, well under a few GB,
     a handful of launches): prefill = 256 clips x 250 frames, one layer; decode = 512 streams on a
-    full ring, one layer.  Prints nothing that is a benchmark value."""
+    full ring, one layer; layer = one whole transformer layer on 256 clips x 250 frames (LayerNorm and the
+    three epilogue variants of the linear kernel); longclip = 16 clips x 2500 frames, three input sets in
+    rotation.  Prints nothing that is a benchmark value."""
     import fast_mimi_b200 as fm
     from fast_mimi_b200 import ops
     dev = torch.device("cuda", 0)
@@ -461,6 +463,18 @@ def profile_case(which: str) -> None:
         cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)
         for _ in range(4):
             ops.attention_prefill(x, w, cos, sin)
+    elif which == "layer":
+        layer = fm.MimiTransformerLayerB200().to(dev)
+        x = torch.randn(256, FRAMES, HIDDEN, device=dev, generator=g)
+        cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)
+        with torch.no_grad():
+            for _ in range(3):
+                layer(x, None, None, (cos, sin), False)
+    elif which == "longclip":
+        sets = [tuple((torch.randn(16, 2500, HIDDEN, device=dev, generator=g) / 8).to(dt)
+                      for dt in (torch.bfloat16, torch.bfloat16, torch.float16)) for _ in range(3)]
+        for i in range(4):
+            ops.band_attention_prefill(*sets[i % 3], window=WINDOW)
     else:
         ring = fm.MimiKVRing(1, 512, WINDOW, device=dev)
         ring.ring_k.copy_((torch.randn(ring.ring_k.shape, device=dev, generator=g) / 2).bfloat16())
@@ -475,7 +489,7 @@ def profile_case(which: str) -> None:
 
 
 def run_extra_workload(args) -> None:
-    """Secondary workloads of BASELINE.json, one JSON line each (single GPU; not the headline line):
+    """Secondary benchmark configurations, one JSON line each (single GPU; not the headline line):
     longclip = config 4 (16 clips x 2500 frames, banded attention alone, rotated BF16 q,k / FP16 v resident);
     stream   = config 5 (4096 streams x 500 one-frame steps x 8 layers from an empty 250-slot ring)."""
     import fast_mimi_b200 as fm
@@ -512,7 +526,7 @@ def run_extra_workload(args) -> None:
         gbs = nbytes / (ms / 1e3) / 1e9
         print(json.dumps({"metric": "attention frames/s", "value": B * T / (ms / 1e3), "unit": "frames/s", "n_gpus": 1,
                           "steps": args.steps, "ms_per_step": ms, "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": "long-clip banded attention (BASELINE config 4), one layer call",
+                          "config": {"workload": "long-clip banded attention (benchmark config 4), one layer call",
                                      "clips": B, "frames": T, "window": WINDOW,
                                      "l2": "three input sets in rotation (492 MB)"},
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -555,7 +569,7 @@ def run_extra_workload(args) -> None:
     gbs = nbytes / (ms / 1e3) / 1e9
     print(json.dumps({"metric": "attention frames/s", "value": S * STEPS * L / (ms / 1e3), "unit": "frames/s", "n_gpus": 1,
                       "steps": STEPS, "ms_total": ms, "ms_per_step": ms / STEPS, "dtype": "bf16", "data": "synthetic",
-                      "config": {"workload": "streaming decode (BASELINE config 5), 500 steps from an empty ring",
+                      "config": {"workload": "streaming decode (benchmark config 5), 500 steps from an empty ring",
                                  "streams": S, "layers": L, "ring_slots": WINDOW, "ring_gb": ring.bytes() / 1e9},
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                    "frac": gbs / peaks["hbm_gbs"], "kernel": "qkv_rope_gemm_kernel + ring_decode_attn_kernel",
@@ -635,7 +649,7 @@ def run_stack(args, dev, peaks, stream, g) -> None:
     print(json.dumps({"metric": "transformer-layer frames/s", "value": rows * LAYERS / (ms / 1e3), "unit": "frames/s",
                       "n_gpus": 1, "steps": args.steps, "ms_per_step": ms, "dtype": "fp16 operands, fp32 accumulate and residual stream",
                       "data": "synthetic",
-                      "config": {"workload": "whole transformer layers over BASELINE config 3's batch", "clips": CLIPS,
+                      "config": {"workload": "whole transformer layers over benchmark config 3's batch", "clips": CLIPS,
                                  "frames": FRAMES, "layers": LAYERS, "launches_per_layer": 7,
                                  "l2": "per-layer tensors (0.26-0.52 GB each) exceed the 126 MB L2"},
                       "step_tflops": total_flop / (ms / 1e3) / 1e12, "frac_tensor": total_flop / (ms / 1e3) / 1e12 / peaks["bf16_tflops"],
@@ -650,7 +664,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
-    ap.add_argument("--profile-case", choices=["prefill", "decode"], help="run a small case for ncu and exit")
+    ap.add_argument("--profile-case", choices=["prefill", "decode", "layer", "longclip"], help="run a small case for ncu and exit")
     ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "stack"],
                     help="prefill = headline (config 3); longclip / stream = configs 4 / 5, stack = whole transformer layers; one extra JSON line each")
     args = ap.parse_args()

@@ -94,7 +94,7 @@ def fill_state_by_recipe(state: dict, seed: int = 0) -> dict:
 
 
 def synthetic_audio(seed: int = 0, seconds: int = 5, rate: int = 24000) -> torch.Tensor:
-    """BASELINE config 1 input: harmonic series f0~U[90,250] Hz, 20 partials at 1/k amplitude, 4 Hz AM
+    """benchmark config 1 input: harmonic series f0~U[90,250] Hz, 20 partials at 1/k amplitude, 4 Hz AM
     envelope, N(0,0.01) noise, normalised to 0.1 RMS; shape [1, 1, seconds*rate]."""
     import math
     g = torch.Generator().manual_seed(seed)

@@ -49,7 +49,7 @@ def save(name, **arrays):
 
 
 def isolated_op():
-    """BASELINE config 2: B=1,H=8,D=64,T=250 FP32 q,k,v ~ N(0,1)/8, RoPE, band mask, SDPA."""
+    """benchmark config 2: B=1,H=8,D=64,T=250 FP32 q,k,v ~ N(0,1)/8, RoPE, band mask, SDPA."""
     cfg = MimiConfig()
     g = torch.Generator().manual_seed(0)
     q, k, v = (torch.randn(1, 8, 250, 64, generator=g) / 8 for _ in range(3))
@@ -182,7 +182,7 @@ def transformer_stack_tiny():
 
 
 def end_to_end_codes(seconds: int = 5):
-    """BASELINE config 1: full Mimi forward on CPU (5 s synthetic audio, 8 codebooks; also 10 s and 12 s, whose
+    """benchmark config 1: full Mimi forward on CPU (5 s synthetic audio, 8 codebooks; also 10 s and 12 s, whose
     250 and 300 transformer frames reach the whole-clip and the long-clip attention kernels) with the weight recipe
     of tests/conftest.py::fill_state_by_recipe, through the reference MimiModel and its functional runtime;
     HF Transformers' MimiModel (the implementation the reference's own tests compare against) is loaded with

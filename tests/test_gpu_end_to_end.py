@@ -1,4 +1,4 @@
-"""BASELINE config 1 end to end: full Mimi encode (SEANet -> 8-layer transformer -> downsample -> RVQ,
+"""benchmark config 1 end to end: full Mimi encode (SEANet -> 8-layer transformer -> downsample -> RVQ,
 8 codebooks) of 5 s of synthetic audio (and of 10 s and 12 s, which reach the other attention kernels) with the
 B200 attention, or the whole B200 transformer layer, swapped into every encoder-transformer layer; RVQ code
 frames must match the reference's CPU result (tests/golden/e2e_codes_*s.npz) on >= 99.5 % of frames (a frame
