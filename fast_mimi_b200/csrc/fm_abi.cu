@@ -37,11 +37,12 @@ int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, voi
 }
 
 int ensure_dynamic_smem(const void* kernel, int bytes) {
-  // cudaFuncSetAttribute is per device; remember which (kernel, device) pairs are done.
-  constexpr int kMaxDev = 64, kMaxKern = 16;
+  // cudaFuncSetAttribute is per device; remember the largest size granted to each (kernel, device) pair
+  // and ask again only for more.
+  constexpr int kMaxDev = 64, kMaxKern = 32;
   static std::mutex mu;
   static const void* kerns[kMaxKern];
-  static bool done[kMaxKern][kMaxDev];
+  static int granted[kMaxKern][kMaxDev];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -51,10 +52,10 @@ int ensure_dynamic_smem(const void* kernel, int bytes) {
     if (kerns[i] == kernel) { slot = i; break; }
     if (kerns[i] == nullptr) { kerns[i] = kernel; slot = i; break; }
   }
-  if (slot >= 0 && dev < kMaxDev && done[slot][dev]) return 0;
+  if (slot >= 0 && dev < kMaxDev && granted[slot][dev] >= bytes) return 0;
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (slot >= 0 && dev < kMaxDev) done[slot][dev] = true;
+  if (slot >= 0 && dev < kMaxDev) granted[slot][dev] = bytes;
   return 0;
 }
 
