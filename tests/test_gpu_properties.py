@@ -108,5 +108,7 @@ def test_prefill_and_decode_replay_inside_a_cuda_graph():
         step.replay()
         eager = ops.decode_step(frame, w, cos[None, t:t + 1], sin[None, t:t + 1], ring_e.ring_k[0], ring_e.ring_v[0], t)
         torch.cuda.synchronize()
-        assert torch.equal(o, eager), t
+        # the eager call knows the position on the host and may take the short-ring kernel: same numbers up to
+        # the order of the FP32 sums
+        assert O.rel_l2(o.cpu(), eager.cpu()) < 1e-5, t
     assert ops.read_status(st) == 0
