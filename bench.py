@@ -502,6 +502,33 @@ def run_extra_workload(args) -> None:
     if args.workload == "stack":
         run_stack(args, dev, peaks, stream, g)
         return
+    if args.workload == "rvq":
+        # the quantiser that follows the encoder transformer: config 3's batch after the stride-2 downsample,
+        # 512 clips x 125 frames = 64 000 vectors of 256 dimensions, 8 codebooks of 2048 entries
+        rows, layers = CLIPS * FRAMES // 2, 8
+        books = ops.RVQCodebooks(torch.randn(layers, 2048, 256, device=dev, generator=g)
+                                 * (0.6 ** torch.arange(layers, device=dev, dtype=torch.float32))[:, None, None])
+        x = torch.randn(rows, 256, device=dev, generator=g) * 1.5
+        for _ in range(max(args.warmup, 3)):
+            codes, cand = ops.rvq_encode(x, books, return_candidates=True)
+        torch.cuda.synchronize()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(args.steps):
+            ops.rvq_encode(x, books)
+        b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        flop = rows * layers * 2 * 2048 * 256
+        nbytes = rows * layers * (2 * 2048 * 4 + 256 * (2 + 4 + 4 + 2))     # scores written + read, residual in both types
+        print(json.dumps({"metric": "quantised vectors/s", "value": rows / (ms / 1e3), "unit": "vectors/s", "n_gpus": 1,
+                          "steps": args.steps, "ms_per_step": ms, "dtype": "fp16 pre-selection, fp32 decision", "data": "synthetic",
+                          "config": {"workload": "residual vector quantisation encode, 8 codebooks x 2048 x 256",
+                                     "vectors": rows, "layers": layers},
+                          "tensor_tflops": flop / (ms / 1e3) / 1e12, "gbs": nbytes / (ms / 1e3) / 1e9,
+                          "frac_hbm": nbytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"],
+                          "exact_evaluations_per_vector_layer": float(cand.float().mean())}))
+        return
     if args.workload == "longclip":
         B, T = 16, 2500
         sets = []
@@ -665,8 +692,8 @@ def main() -> None:
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
     ap.add_argument("--profile-case", choices=["prefill", "decode", "layer", "longclip"], help="run a small case for ncu and exit")
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "stack"],
-                    help="prefill = headline (config 3); longclip / stream = configs 4 / 5, stack = whole transformer layers; one extra JSON line each")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "stack", "rvq"],
+                    help="prefill = headline (config 3); longclip / stream = configs 4 / 5, stack = whole transformer layers, rvq = the quantiser after the encoder transformer; one extra JSON line each")
     args = ap.parse_args()
     if args.profile_case:
         profile_case(args.profile_case)

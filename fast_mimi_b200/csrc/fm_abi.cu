@@ -117,6 +117,22 @@ int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const floa
   return fm::launch_layernorm512(x, x_dtype, weight, bias, eps, y, y_dtype, rows, static_cast<cudaStream_t>(stream));
 }
 
+int fm_rvq_select_f32(const float* scores, const float* e_sq, const float* codebook, float* residual, void* residual16,
+                      long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
+                      void* stream) {
+  return fm::launch_rvq_select(scores, e_sq, codebook, residual, residual16, codes, n_candidates, rows, n_codes, e_max,
+                               tau_rel, static_cast<cudaStream_t>(stream));
+}
+
+int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream) {
+  return fm::launch_rvq_to_half(x, y, rows, static_cast<cudaStream_t>(stream));
+}
+
+int fm_rvq_decode_f32(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
+                      int n_codes, int* bad_code, void* stream) {
+  return fm::launch_rvq_decode(codes, codebooks, out, rows, n_layers, n_codes, bad_code, static_cast<cudaStream_t>(stream));
+}
+
 int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring_v, float* out,
                              const int* stream_pos, int pos_base, int S, int ring_slots, float scale,
                              int value_dtype, int* status, void* stream) {

@@ -57,6 +57,14 @@ int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale
 // LayerNorm over 512 channels; x_dtype 0 BF16 / 1 FP16 / 2 FP32, y_dtype 0 BF16 / 1 FP16.
 int launch_layernorm512(const void* x, int x_dtype, const float* weight, const float* bias, float eps, void* y,
                         int y_dtype, long long rows, cudaStream_t st);
+// Residual vector quantisation (fm_rvq.cu): candidate selection + exact FP32 decision for one layer, FP16 copy of
+// the residual, ordered FP32 decode.
+int launch_rvq_select(const float* scores, const float* e_sq, const float* codebook, float* resid, void* resid16,
+                      long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
+                      cudaStream_t st);
+int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st);
+int launch_rvq_decode(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
+                      int n_codes, int* bad_code, cudaStream_t st);
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st);
 int launch_band_attn_clip(const void* q, const void* k, const void* v, void* out, int B, int T, int window,

@@ -1,0 +1,206 @@
+// Residual vector quantisation around the encoder transformer (sm_100a): nearest-codebook search and ordered
+// decode for Mimi's Euclidean codebooks (2048 entries of 256 dimensions per layer).
+//
+// Reference: MimiEuclideanCodebook.quantize = argmin over torch.cdist (src/fast_mimi/model.py:2277-2291),
+// MimiResidualVectorQuantizer.encode subtracts the chosen entry before the next layer's search
+// (src/fast_mimi/model.py:2408-2429), decode adds the layers' entries left to right starting from an FP32 zero
+// (src/fast_mimi/model.py:2431-2444).
+//
+// Search: the 2048 inner products per frame are a GEMM and run on the tensor core with FP16 operands (the general
+// linear kernel of this library, K = 256, N = 2048).  They only PRE-SELECT: for a frame x the approximate
+// distances  |e_j|^2 - 2 x.e_j  differ from the exact ones by at most  tau = tau_rel * |x| * max_j |e_j|
+// (operand rounding 2^-11 each, FP32 accumulation), so every entry within tau of the approximate minimum is a
+// candidate and the entry that wins is decided among the candidates by the exact FP32 distance
+// sum_k (x_k - e_jk)^2, lowest index on ties (argmin's rule).  rvq_select_kernel does that per frame with one
+// warp, writes the code, subtracts the entry from the residual (FP32, in place) and emits the FP16 copy of the
+// new residual that the next layer's GEMM consumes.
+#include "fm_common.cuh"
+#include "fm_kernels.h"
+
+namespace fm {
+
+namespace rvq {
+constexpr int kDim = 256;        // codebook dimension
+constexpr int kWarps = 8;        // warps (frames in flight) per block
+}  // namespace rvq
+
+__global__ void __launch_bounds__(rvq::kWarps * 32)
+rvq_select_kernel(const float* __restrict__ scores, const float* __restrict__ e_sq, const float* __restrict__ codebook,
+                  float* __restrict__ resid, uint16_t* __restrict__ resid16, long long* __restrict__ codes,
+                  int* __restrict__ n_candidates, long long rows, int n_codes, float e_max, float tau_rel) {
+  using namespace rvq;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+  for (long long row = warp0; row < rows; row += stride) {
+    // this lane's 8 residual values (dimensions 8 * lane .. 8 * lane + 7)
+    float x[8];
+    {
+      const float4* xr = reinterpret_cast<const float4*>(resid + row * kDim + lane * 8);
+      const float4 a = xr[0], b = xr[1];
+      x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+    float xx = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) xx = fmaf(x[k], x[k], xx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) xx += __shfl_xor_sync(0xffffffffu, xx, o);
+    // relative part: FP16 rounding of both operands; absolute part: residual values below FP16's normal range
+    const float tau = tau_rel * sqrtf(xx) * e_max + 3.1e-5f * e_max;
+
+    // pass A: minimum of the approximate distances
+    const float4* s4 = reinterpret_cast<const float4*>(scores + row * n_codes);
+    const float4* q4 = reinterpret_cast<const float4*>(e_sq);
+    const int n_vec = n_codes >> 2;                  // float4 groups per row
+    float d_min = INFINITY;
+    for (int v = lane; v < n_vec; v += 32) {
+      const float4 s = s4[v], q = __ldg(q4 + v);
+      d_min = fminf(d_min, fminf(fminf(fmaf(-2.f, s.x, q.x), fmaf(-2.f, s.y, q.y)),
+                                 fminf(fmaf(-2.f, s.z, q.z), fmaf(-2.f, s.w, q.w))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d_min = fminf(d_min, __shfl_xor_sync(0xffffffffu, d_min, o));
+    const float limit = d_min + tau;
+
+    // pass B: exact distance of every candidate, in ascending index order
+    float best = INFINITY;
+    int best_j = 0, n_cand = 0;
+    for (int v0 = 0; v0 < n_vec; v0 += 32) {
+      const int v = v0 + lane;
+      float d[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
+      if (v < n_vec) {
+        const float4 s = s4[v], q = __ldg(q4 + v);
+        d[0] = fmaf(-2.f, s.x, q.x); d[1] = fmaf(-2.f, s.y, q.y); d[2] = fmaf(-2.f, s.z, q.z); d[3] = fmaf(-2.f, s.w, q.w);
+      }
+      // candidates of this group of 128 entries: bit (4 * lane + e) of a 128-bit set, walked in index order
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        unsigned mask = __ballot_sync(0xffffffffu, d[e] <= limit);
+        while (mask != 0u) {
+          const int src = __ffs(mask) - 1;
+          mask &= mask - 1u;
+          const int j = (v0 + src) * 4 + e;
+          const float4* er = reinterpret_cast<const float4*>(codebook + static_cast<size_t>(j) * kDim + lane * 8);
+          const float4 a = __ldg(er), b = __ldg(er + 1);
+          const float ev[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+          float acc = 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float t = x[k] - ev[k];
+            acc = fmaf(t, t, acc);
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+          ++n_cand;
+          // Within one (e) sweep indices ascend with the lane; across the four sweeps of a group they interleave,
+          // so ties are resolved explicitly in favour of the lower index.
+          if (acc < best || (acc == best && j < best_j)) {
+            best = acc;
+            best_j = j;
+          }
+        }
+      }
+    }
+
+    // the chosen entry leaves the residual; the next layer's GEMM reads the FP16 copy
+    {
+      const float4* er = reinterpret_cast<const float4*>(codebook + static_cast<size_t>(best_j) * kDim + lane * 8);
+      const float4 a = __ldg(er), b = __ldg(er + 1);
+      const float ev[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) x[k] -= ev[k];
+      float4* xw = reinterpret_cast<float4*>(resid + row * kDim + lane * 8);
+      xw[0] = make_float4(x[0], x[1], x[2], x[3]);
+      xw[1] = make_float4(x[4], x[5], x[6], x[7]);
+      *reinterpret_cast<uint4*>(resid16 + row * kDim + lane * 8) =
+          make_uint4(Pack16<__half>::pack(x[0], x[1]), Pack16<__half>::pack(x[2], x[3]), Pack16<__half>::pack(x[4], x[5]),
+                     Pack16<__half>::pack(x[6], x[7]));
+    }
+    if (lane == 0) {
+      codes[row] = best_j;
+      if (n_candidates != nullptr) n_candidates[row] = n_cand;
+    }
+  }
+}
+
+// FP32 -> FP16 copy of the residual before the first layer (256 values per frame).
+__global__ void __launch_bounds__(256)
+rvq_to_half_kernel(const float* __restrict__ x, uint16_t* __restrict__ y, long long n8) {
+  const long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = i0; i < n8; i += stride) {
+    const float4 a = reinterpret_cast<const float4*>(x)[2 * i], b = reinterpret_cast<const float4*>(x)[2 * i + 1];
+    reinterpret_cast<uint4*>(y)[i] = make_uint4(Pack16<__half>::pack(a.x, a.y), Pack16<__half>::pack(a.z, a.w),
+                                                Pack16<__half>::pack(b.x, b.y), Pack16<__half>::pack(b.z, b.w));
+  }
+}
+
+// out[row, :] = ((0 + E_0[c_0]) + E_1[c_1]) + ...  in FP32, layers left to right.
+__global__ void __launch_bounds__(256)
+rvq_decode_kernel(const long long* __restrict__ codes, const float* __restrict__ codebooks, float* __restrict__ out,
+                  long long rows, int n_layers, int n_codes, int* __restrict__ bad_code) {
+  using namespace rvq;
+  const int sub = threadIdx.x & 63;                 // 64 threads per frame, 4 dimensions each
+  const long long row0 = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 6);
+  const long long stride = static_cast<long long>(gridDim.x) * 4;
+  for (long long row = row0; row < rows; row += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int l = 0; l < n_layers; ++l) {
+      long long cidx = codes[static_cast<long long>(l) * rows + row];
+      if (cidx < 0 || cidx >= n_codes) {            // recorded, not dereferenced
+        if (bad_code != nullptr) atomicExch(bad_code, 1);
+        cidx = 0;
+      }
+      const float4 e = __ldg(reinterpret_cast<const float4*>(
+          codebooks + (static_cast<size_t>(l) * n_codes + static_cast<size_t>(cidx)) * kDim + sub * 4));
+      acc.x += e.x; acc.y += e.y; acc.z += e.z; acc.w += e.w;
+    }
+    reinterpret_cast<float4*>(out + row * kDim)[sub] = acc;
+  }
+}
+
+static int grid_for(long long work_blocks, int per_sm) {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long cap = static_cast<long long>(sms > 0 ? sms : 1) * per_sm;
+  const long long g = work_blocks < cap ? work_blocks : cap;
+  return static_cast<int>(g > 0 ? g : 1);
+}
+
+int launch_rvq_select(const float* scores, const float* e_sq, const float* codebook, float* resid, void* resid16,
+                      long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
+                      cudaStream_t st) {
+  if (rows < 0 || n_codes <= 0 || n_codes % 4 != 0 || !(e_max >= 0.f) || !(tau_rel >= 0.f)) return -1;
+  if (rows == 0) return 0;
+  if (scores == nullptr || e_sq == nullptr || codebook == nullptr || resid == nullptr || resid16 == nullptr || codes == nullptr)
+    return -1;
+  if ((reinterpret_cast<uintptr_t>(scores) | reinterpret_cast<uintptr_t>(e_sq) | reinterpret_cast<uintptr_t>(codebook) |
+       reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(resid16)) & 15u)
+    return -3;
+  const int grid = grid_for((rows + rvq::kWarps - 1) / rvq::kWarps, 8);
+  rvq_select_kernel<<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16), codes,
+                                                      n_candidates, rows, n_codes, e_max, tau_rel);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st) {
+  if (rows < 0) return -1;
+  if (rows == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) return -3;
+  const long long n8 = rows * (rvq::kDim / 8);
+  rvq_to_half_kernel<<<grid_for((n8 + 255) / 256, 8), 256, 0, st>>>(x, static_cast<uint16_t*>(y), n8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_rvq_decode(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers, int n_codes,
+                      int* bad_code, cudaStream_t st) {
+  if (rows < 0 || n_layers <= 0 || n_codes <= 0) return -1;
+  if (rows == 0) return 0;
+  if (codes == nullptr || codebooks == nullptr || out == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(codebooks) | reinterpret_cast<uintptr_t>(out)) & 15u) return -3;
+  rvq_decode_kernel<<<grid_for((rows + 3) / 4, 8), 256, 0, st>>>(codes, codebooks, out, rows, n_layers, n_codes, bad_code);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fm

@@ -398,3 +398,67 @@ def rope_fp32_(t, cos, sin):
     rc = lib.fm_rope_fp32_verify(t.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, T, H, D, bstride, _stream())
     _native.check(rc, "fm_rope_fp32_verify")
     return t
+
+
+# --------------------------------------------------------------------------- residual vector quantisation
+RVQ_DIM = 256
+RVQ_TAU_REL = 4.5e-3     # covers the FP16 rounding of both operands of the pre-selecting inner products
+
+
+class RVQCodebooks:
+    """Device-side constants of a residual quantiser stack, derived once from its codebook vectors
+    ``[layers, entries, 256]`` float32 (the reference's ``MimiEuclideanCodebook.embed`` of every layer,
+    src/fast_mimi/model.py:2262-2275): FP16 copies for the tensor core, squared norms, largest norm."""
+
+    def __init__(self, codebooks: torch.Tensor) -> None:
+        _need(codebooks.is_cuda and codebooks.dtype == torch.float32 and codebooks.dim() == 3
+              and codebooks.shape[2] == RVQ_DIM and codebooks.shape[1] % 256 == 0,
+              "codebooks must be CUDA float32 [layers, entries (multiple of 256), 256]")
+        self.vectors = codebooks.contiguous()
+        self.half = self.vectors.half().contiguous()
+        self.sq = (self.vectors.double() ** 2).sum(-1).float().contiguous()           # [layers, entries]
+        self.e_max = [float(v) for v in self.sq.max(dim=1).values.sqrt().cpu()]
+        self.layers, self.entries = codebooks.shape[0], codebooks.shape[1]
+
+
+def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates=False, status=None):
+    """Codes ``[layers, rows]`` int64 of the residual quantiser stack for ``x [rows, 256]`` float32 (the output
+    of the branch's ``input_proj``).  Per layer: inner products with all entries on the tensor core (FP16
+    operands) pre-select, the exact FP32 distance decides among the candidates, the chosen entry is subtracted.
+    ``x`` is not modified."""
+    lib = _native.load()
+    _need(x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] == RVQ_DIM, "x must be CUDA float32 [rows, 256]")
+    layers = books.layers if num_quantizers is None else int(num_quantizers)
+    _need(0 < layers <= books.layers, "num_quantizers out of range")
+    rows = x.shape[0]
+    resid = x.contiguous().clone()
+    resid16 = torch.empty(rows, RVQ_DIM, dtype=torch.float16, device=x.device)
+    scores = torch.empty(rows, books.entries, dtype=torch.float32, device=x.device)
+    codes = torch.empty(layers, rows, dtype=torch.int64, device=x.device)
+    cand = torch.empty(layers, rows, dtype=torch.int32, device=x.device) if return_candidates else None
+    _native.check(lib.fm_rvq_to_half(resid.data_ptr(), resid16.data_ptr(), rows, _stream()), "fm_rvq_to_half")
+    for l in range(layers):
+        linear(resid16, books.half[l], out_dtype=torch.float32, out=scores, status=status)
+        rc = lib.fm_rvq_select_f32(scores.data_ptr(), books.sq[l].data_ptr(), books.vectors[l].data_ptr(), resid.data_ptr(),
+                                   resid16.data_ptr(), codes[l].data_ptr(), cand[l].data_ptr() if cand is not None else None,
+                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL, _stream())
+        _native.check(rc, "fm_rvq_select_f32")
+    return (codes, cand) if return_candidates else codes
+
+
+def rvq_decode(codes, books: RVQCodebooks):
+    """``sum_l E_l[codes[l]]`` as float32 ``[rows, 256]``, layers added left to right from an FP32 zero (the
+    accumulation order of the reference's decode, src/fast_mimi/model.py:2431-2444, before ``output_proj``)."""
+    lib = _native.load()
+    _need(codes.is_cuda and codes.dtype == torch.int64 and codes.dim() == 2 and codes.is_contiguous(),
+          "codes must be contiguous CUDA int64 [layers, rows]")
+    layers, rows = codes.shape
+    _need(0 < layers <= books.layers, "more code layers than codebooks")
+    out = torch.empty(rows, RVQ_DIM, dtype=torch.float32, device=codes.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=codes.device)
+    rc = lib.fm_rvq_decode_f32(codes.data_ptr(), books.vectors.data_ptr(), out.data_ptr(), rows, layers, books.entries,
+                               bad.data_ptr(), _stream())
+    _native.check(rc, "fm_rvq_decode_f32")
+    if int(bad.item()) != 0:
+        raise RuntimeError("rvq_decode: a code index is outside the codebook")
+    return out

@@ -77,6 +77,32 @@ int fm_linear_f16(const void* a, const void* w, const float* scale, const void* 
 int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const float* bias, float eps, void* y,
                      int y_dtype, long long rows, void* stream);
 
+/* One layer of residual vector quantisation for `rows` frames of 256 dimensions against a codebook of n_codes
+ * entries: replaces MimiEuclideanCodebook.quantize (argmin over torch.cdist, src/fast_mimi/model.py:2277-2291) and
+ * the residual update of MimiResidualVectorQuantizer.encode (src/fast_mimi/model.py:2420-2427).
+ *   scores    [rows, n_codes] FP32: inner products residual . e_j computed from FP16 copies of both (fm_linear_f16
+ *             with a = residual16, w = FP16 codebook, FP32 output); they pre-select only
+ *   e_sq      [n_codes] FP32: |e_j|^2      codebook [n_codes, 256] FP32      e_max = max_j |e_j|
+ *   residual  [rows, 256] FP32, in/out: the chosen entry is subtracted
+ *   residual16 [rows, 256] FP16 out: copy of the new residual for the next layer's inner products
+ *   codes     [rows] int64 out        n_candidates [rows] int32 out or NULL (entries that were decided exactly)
+ * Every entry whose approximate distance is within tau_rel * |residual| * e_max of the minimum is re-evaluated as
+ * sum_k (x_k - e_jk)^2 in FP32; the smallest wins, the lowest index on ties.  tau_rel = 4.5e-3 covers the FP16
+ * operand rounding. */
+int fm_rvq_select_f32(const float* scores, const float* e_sq, const float* codebook, float* residual,
+                      void* residual16, long long* codes, int* n_candidates, long long rows, int n_codes,
+                      float e_max, float tau_rel, void* stream);
+
+/* FP16 copy of [rows, 256] FP32 values (the residual before the first layer). */
+int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream);
+
+/* out[row] = ((0 + E_0[codes[0,row]]) + E_1[codes[1,row]]) + ... in FP32, layers left to right, as
+ * MimiResidualVectorQuantizer.decode does before output_proj (src/fast_mimi/model.py:2431-2444).
+ *   codes [n_layers, rows] int64      codebooks [n_layers, n_codes, 256] FP32      out [rows, 256] FP32
+ *   bad_code: optional device int set to 1 when an index is out of range (that index is then read as 0). */
+int fm_rvq_decode_f32(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
+                      int n_codes, int* bad_code, void* stream);
+
 /* fm_qkv_rope_bf16 followed by fm_band_attn_prefill_bf16 on the same stream: the part of
  * MimiAttention.forward between the input and o_proj (src/fast_mimi/model.py:1896-1951) for a call
  * without cache.  q_ws/k_ws/v_ws are caller-provided workspaces of B*T*512 16-bit elements each. */

@@ -106,3 +106,14 @@ def synthetic_audio(seed: int = 0, seconds: int = 5, rate: int = 24000) -> torch
     sig = sig + 0.01 * torch.randn(n, generator=g, dtype=torch.float64)
     sig = sig * (0.1 / sig.pow(2).mean().sqrt())
     return sig.float().view(1, 1, n)
+
+
+def rvq_recipe(seed: int, layers: int, entries: int = 2048, dim: int = 256, hidden: int = 512):
+    """Seeded residual-quantiser constants: codebook buffers as the reference's own fixture randomises them
+    (embed_sum ~ N(0,1), cluster_usage ~ U[0.5,1.5); tests/conftest.py:41-53 of the reference), an input
+    projection ~ N(0, 1/hidden) and embeddings are drawn by the caller from the same generator."""
+    g = torch.Generator().manual_seed(seed)
+    embed_sum = torch.randn(layers, entries, dim, generator=g)
+    usage = torch.rand(layers, entries, generator=g) + 0.5
+    proj = torch.randn(dim, hidden, generator=g) / hidden ** 0.5
+    return g, embed_sum, usage, proj

@@ -220,6 +220,33 @@ def end_to_end_codes(seconds: int = 5):
     print("codes", tuple(codes.shape), "distinct", len(torch.unique(codes)))
 
 
+def rvq_codes():
+    """Residual quantiser stack of the reference (7 layers, 2048 x 256 codebooks, 1x1 input projection) on seeded
+    embeddings [2, 512, 40]: codes, and the decoded sum before the output projection at a few frames."""
+    sys.path.insert(0, os.path.dirname(HERE))
+    from conftest import rvq_recipe
+    from fast_mimi.model import MimiResidualVectorQuantizer
+    cfg = MimiConfig()
+    layers = 7
+    g, embed_sum, usage, proj = rvq_recipe(31, layers)
+    emb = torch.randn(2, cfg.hidden_size, 40, generator=g) * 3
+    rvq = MimiResidualVectorQuantizer(cfg, layers).eval()
+    with torch.no_grad():
+        rvq.input_proj.weight.copy_(proj[:, :, None])
+        for i, layer in enumerate(rvq.layers):
+            layer.codebook.embed_sum.copy_(embed_sum[i])
+            layer.codebook.cluster_usage.copy_(usage[i])
+            layer.codebook._embed = None
+    with torch.inference_mode():
+        codes = rvq.encode(emb)                                   # [layers, 2, 40]
+        quantized = codes.new_zeros((), dtype=torch.float32)
+        for index, indices in enumerate(codes):
+            quantized = quantized + rvq.layers[index].decode(indices)   # [2, 256, 40]
+    save("rvq_codes.npz", codes=codes, quantized_probe=quantized[:, :, ::13], emb_probe=emb[0, :4, :4],
+         distinct=len(torch.unique(codes)))
+    print("rvq codes", tuple(codes.shape), "distinct", len(torch.unique(codes)))
+
+
 if __name__ == "__main__":
     isolated_op()
     long_band()
@@ -237,3 +264,4 @@ if __name__ == "__main__":
     transformer_stack_tiny()
     for seconds in (5, 10, 12):
         end_to_end_codes(seconds)
+    rvq_codes()

@@ -122,3 +122,20 @@ def test_layer_block_restatements_equal_the_library_calls_the_reference_makes():
     assert torch.equal(O.mlp(x, fc1, fc2), F.linear(F.gelu(F.linear(x, fc1)), fc2))
     wo, s = torch.randn(512, 512, generator=g) * 0.04, torch.rand(512, generator=g)
     assert torch.equal(O.out_proj_residual(x, wo, s, x), x + F.linear(x, wo) * s)
+
+
+def test_rvq_restatement_matches_the_reference_quantizer():
+    """oracle.rvq_encode / rvq_decode against codes and decoded sums that the reference's
+    MimiResidualVectorQuantizer produced (tests/golden/rvq_codes.npz) for the same seeded constants."""
+    import torch.nn.functional as F
+    from conftest import rvq_recipe
+    g = load_golden("rvq_codes.npz")
+    gen, embed_sum, usage, proj = rvq_recipe(31, 7)
+    emb = torch.randn(2, 512, 40, generator=gen) * 3
+    assert torch.equal(emb[0, :4, :4], g["emb_probe"])
+    books = embed_sum / usage.clamp(min=1e-5)[:, :, None]
+    x = F.conv1d(emb, proj[:, :, None]).permute(0, 2, 1).reshape(-1, 256)       # input_proj, frames as rows
+    codes = O.rvq_encode(x, books).view(7, 2, 40)
+    assert torch.equal(codes, g["codes"])
+    dec = O.rvq_decode(codes.view(7, 80), books).view(2, 40, 256).permute(0, 2, 1)
+    assert torch.equal(dec[:, :, ::13], g["quantized_probe"])
