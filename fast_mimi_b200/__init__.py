@@ -6,6 +6,7 @@ Public surface:
   window_attention_nlc     drop-in for the reference's long-sequence ``_window_attention_nlc`` ([B, T, 512] result)
   rope_tables              the FP32 cos / sin tables of the reference's ``MimiRotaryEmbedding``
   MimiTransformerLayerB200 drop-in for the reference's ``MimiTransformerLayer`` (whole layer on these kernels)
+  MimiSplitRVQB200         encode / decode of the reference's split residual vector quantiser
   MimiKVRing               streaming KV state with ``MimiKVCache``'s bookkeeping interface
   ops                      tensor-level wrappers over the C ABI (include/fast_mimi_b200.h)
 """
@@ -14,7 +15,8 @@ from .attention import (MimiAttentionB200, install, native_window_attention, rop
                         window_attention_nlc)
 from .kv_ring import LinearKVCache, MimiKVRing
 from .layer import MimiTransformerLayerB200, install_layers
+from .rvq import MimiRVQB200, MimiSplitRVQB200
 from .sharding import gather_to_host, shard, shard_bounds
 
-__all__ = ["MimiAttentionB200", "MimiTransformerLayerB200", "install_layers", "MimiKVRing", "LinearKVCache", "install", "native_window_attention",
+__all__ = ["MimiAttentionB200", "MimiTransformerLayerB200", "install_layers", "MimiRVQB200", "MimiSplitRVQB200", "MimiKVRing", "LinearKVCache", "install", "native_window_attention",
            "window_attention_fp32", "window_attention_nlc", "rope_tables", "ops", "shard", "shard_bounds", "gather_to_host"]

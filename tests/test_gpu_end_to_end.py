@@ -69,7 +69,7 @@ def _frame_agreement(a: torch.Tensor, b: torch.Tensor) -> float:
 
 
 @pytest.mark.parametrize("seconds", [5, 10, 12])     # 125, 250, 300 transformer frames: general, whole-clip, long-clip kernel
-@pytest.mark.parametrize("swap", ["attention", "layers"])
+@pytest.mark.parametrize("swap", ["attention", "layers", "layers+rvq"])
 def test_rvq_codes_match_reference_with_b200_attention(swap, seconds):
     from transformers import MimiConfig as HFConfig, MimiModel as HFModel
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -96,6 +96,9 @@ def test_rvq_codes_match_reference_with_b200_attention(swap, seconds):
                 layer.self_attn = _HFAttentionAdapter(layer.self_attn, layer_idx)
             else:        # LayerNorms, projections, attention, MLP, layer scales and residual adds: all native
                 layers[layer_idx] = _HFLayerAdapter(layer)
+        if swap == "layers+rvq":     # ... and the quantiser behind the transformer as well
+            import fast_mimi_b200 as fm
+            model.quantizer.encode = fm.MimiSplitRVQB200.from_reference(model.quantizer).encode
         ours = model.encode(audio, num_quantizers=8).audio_codes.cpu()
     golden = g["codes"]
     assert ours.shape == golden.shape == (1, 8, (seconds * 25 + 1) // 2)

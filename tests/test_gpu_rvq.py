@@ -54,3 +54,54 @@ def test_rvq_decode_rejects_out_of_range_codes():
     codes = torch.tensor([[0, 5], [256, 1]], dtype=torch.int64).cuda()
     with pytest.raises(RuntimeError):
         fm.ops.rvq_decode(codes, gb)
+
+
+def test_split_quantizer_wrapper_matches_oracle_encode_and_decode():
+    """MimiSplitRVQB200 built from modules that carry the reference's attribute names (layers[i].codebook.embed,
+    1 x 1 input_proj / output_proj): encode codes and decode output against the oracle with the same projections."""
+    import types
+    import torch.nn as nn
+    import fast_mimi_b200 as fm
+
+    def branch(seed, layers):
+        gen, embed_sum, usage, proj = rvq_recipe(seed, layers)
+        books = _books(embed_sum, usage)
+        mod = types.SimpleNamespace()
+        mod.layers = [types.SimpleNamespace(codebook=types.SimpleNamespace(embed=books[i].cuda())) for i in range(layers)]
+        mod.input_proj = nn.Conv1d(512, 256, 1, bias=False)
+        mod.output_proj = nn.Conv1d(256, 512, 1, bias=False)
+        with torch.no_grad():
+            mod.input_proj.weight.copy_(proj[:, :, None])
+            mod.output_proj.weight.copy_(torch.randn(512, 256, 1, generator=gen) / 16)
+        mod.input_proj.cuda(); mod.output_proj.cuda()
+        return mod, books
+
+    sem, sem_books = branch(41, 1)
+    aco, aco_books = branch(42, 7)
+    split = types.SimpleNamespace(semantic_residual_vector_quantizer=sem, acoustic_residual_vector_quantizer=aco)
+    native = fm.MimiSplitRVQB200.from_reference(split)
+    emb = torch.randn(3, 512, 50, generator=torch.Generator().manual_seed(43)) * 3
+
+    def oracle_encode(mod, books, n):
+        x = F.conv1d(emb, mod.input_proj.weight.cpu()).permute(0, 2, 1).reshape(-1, 256)
+        return O.rvq_encode(x, books, n).view(n, 3, 50)
+
+    want = torch.cat((oracle_encode(sem, sem_books, 1), oracle_encode(aco, aco_books, 7)))
+    got = native.encode(emb.cuda(), 8).cpu()
+    assert got.shape == (8, 3, 50)
+    assert (got == want).all(dim=0).float().mean() >= 0.995
+    assert torch.equal(native.encode(emb.cuda(), 3).cpu(), got[:3])
+
+    codes = got.permute(1, 0, 2).contiguous()                       # [B, K, T] as the reference's decode takes them
+    dec = native.decode(codes.cuda()).cpu()
+
+    def oracle_decode(mod, books, c):                               # c [K, B*T]
+        q = O.rvq_decode(c, books).view(3, 50, 256).permute(0, 2, 1)
+        return F.conv1d(q, mod.output_proj.weight.cpu())
+
+    flat = got.reshape(8, -1)
+    ref = oracle_decode(sem, sem_books, flat[:1]) + oracle_decode(aco, aco_books, flat[1:])
+    assert dec.shape == (3, 512, 50)
+    assert O.rel_l2(dec, ref) < 1e-5
+    with pytest.raises(ValueError):
+        native.encode(emb.cuda(), 0)
