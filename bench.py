@@ -520,7 +520,7 @@ def run_extra_workload(args) -> None:
         torch.cuda.synchronize()
         ms = a.elapsed_time(b) / args.steps
         flop = rows * layers * 2 * 2048 * 256
-        nbytes = rows * layers * (2 * 2048 * 4 + 256 * (2 + 4 + 4 + 2))     # scores written + read, residual in both types
+        nbytes = rows * layers * (2 * 2048 * 2 + 256 * (2 + 4 + 4 + 2))     # FP16 scores written + read, residual in both types
         print(json.dumps({"metric": "quantised vectors/s", "value": rows / (ms / 1e3), "unit": "vectors/s", "n_gpus": 1,
                           "steps": args.steps, "ms_per_step": ms, "dtype": "fp16 pre-selection, fp32 decision", "data": "synthetic",
                           "config": {"workload": "residual vector quantisation encode, 8 codebooks x 2048 x 256",

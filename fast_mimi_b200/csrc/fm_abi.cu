@@ -117,10 +117,11 @@ int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const floa
   return fm::launch_layernorm512(x, x_dtype, weight, bias, eps, y, y_dtype, rows, static_cast<cudaStream_t>(stream));
 }
 
-int fm_rvq_select_f32(const float* scores, const float* e_sq, const float* codebook, float* residual, void* residual16,
-                      long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
-                      void* stream) {
-  return fm::launch_rvq_select(scores, e_sq, codebook, residual, residual16, codes, n_candidates, rows, n_codes, e_max,
+int fm_rvq_select_f32(const void* scores, int scores_dtype, const float* e_sq, const float* codebook, float* residual,
+                      void* residual16, long long* codes, int* n_candidates, long long rows, int n_codes, float e_max,
+                      float tau_rel, void* stream) {
+  if (scores_dtype != 1 && scores_dtype != 2) return -1;
+  return fm::launch_rvq_select(scores, scores_dtype == 1, e_sq, codebook, residual, residual16, codes, n_candidates, rows, n_codes, e_max,
                                tau_rel, static_cast<cudaStream_t>(stream));
 }
 

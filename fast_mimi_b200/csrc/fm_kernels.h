@@ -59,7 +59,7 @@ int launch_layernorm512(const void* x, int x_dtype, const float* weight, const f
                         int y_dtype, long long rows, cudaStream_t st);
 // Residual vector quantisation (fm_rvq.cu): candidate selection + exact FP32 decision for one layer, FP16 copy of
 // the residual, ordered FP32 decode.
-int launch_rvq_select(const float* scores, const float* e_sq, const float* codebook, float* resid, void* resid16,
+int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, const float* codebook, float* resid, void* resid16,
                       long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
                       cudaStream_t st);
 int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st);

@@ -9,7 +9,8 @@
 // Search: the 2048 inner products per frame are a GEMM and run on the tensor core with FP16 operands (the general
 // linear kernel of this library, K = 256, N = 2048).  They only PRE-SELECT: for a frame x the approximate
 // distances  |e_j|^2 - 2 x.e_j  differ from the exact ones by at most  tau = tau_rel * |x| * max_j |e_j|
-// (operand rounding 2^-11 each, FP32 accumulation), so every entry within tau of the approximate minimum is a
+// (operand rounding 2^-11 each, FP32 accumulation, plus another 2^-11 when the scores are stored as FP16), so every
+// entry within tau of the approximate minimum is a
 // candidate and the entry that wins is decided among the candidates by the exact FP32 distance
 // sum_k (x_k - e_jk)^2, lowest index on ties (argmin's rule).  rvq_select_kernel does that per frame with one
 // warp, writes the code, subtracts the entry from the residual (FP32, in place) and emits the FP16 copy of the
@@ -24,8 +25,23 @@ constexpr int kDim = 256;        // codebook dimension
 constexpr int kWarps = 8;        // warps (frames in flight) per block
 }  // namespace rvq
 
+namespace rvq {
+// Four consecutive scores of a row, stored as FP32 or as FP16.
+template <bool kHalf>
+__device__ __forceinline__ float4 load_scores4(const void* row_base, int v) {
+  if constexpr (kHalf) {
+    const uint2 u = reinterpret_cast<const uint2*>(row_base)[v];
+    const float2 a = Pack16<__half>::unpack(u.x), b = Pack16<__half>::unpack(u.y);
+    return make_float4(a.x, a.y, b.x, b.y);
+  } else {
+    return reinterpret_cast<const float4*>(row_base)[v];
+  }
+}
+}  // namespace rvq
+
+template <bool kHalf>
 __global__ void __launch_bounds__(rvq::kWarps * 32)
-rvq_select_kernel(const float* __restrict__ scores, const float* __restrict__ e_sq, const float* __restrict__ codebook,
+rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_sq, const float* __restrict__ codebook,
                   float* __restrict__ resid, uint16_t* __restrict__ resid16, long long* __restrict__ codes,
                   int* __restrict__ n_candidates, long long rows, int n_codes, float e_max, float tau_rel) {
   using namespace rvq;
@@ -49,12 +65,12 @@ rvq_select_kernel(const float* __restrict__ scores, const float* __restrict__ e_
     const float tau = tau_rel * sqrtf(xx) * e_max + 3.1e-5f * e_max;
 
     // pass A: minimum of the approximate distances
-    const float4* s4 = reinterpret_cast<const float4*>(scores + row * n_codes);
+    const void* s4 = static_cast<const uint8_t*>(scores) + static_cast<size_t>(row) * n_codes * (kHalf ? 2 : 4);
     const float4* q4 = reinterpret_cast<const float4*>(e_sq);
     const int n_vec = n_codes >> 2;                  // float4 groups per row
     float d_min = INFINITY;
     for (int v = lane; v < n_vec; v += 32) {
-      const float4 s = s4[v], q = __ldg(q4 + v);
+      const float4 s = load_scores4<kHalf>(s4, v), q = __ldg(q4 + v);
       d_min = fminf(d_min, fminf(fminf(fmaf(-2.f, s.x, q.x), fmaf(-2.f, s.y, q.y)),
                                  fminf(fmaf(-2.f, s.z, q.z), fmaf(-2.f, s.w, q.w))));
     }
@@ -69,7 +85,7 @@ rvq_select_kernel(const float* __restrict__ scores, const float* __restrict__ e_
       const int v = v0 + lane;
       float d[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
       if (v < n_vec) {
-        const float4 s = s4[v], q = __ldg(q4 + v);
+        const float4 s = load_scores4<kHalf>(s4, v), q = __ldg(q4 + v);
         d[0] = fmaf(-2.f, s.x, q.x); d[1] = fmaf(-2.f, s.y, q.y); d[2] = fmaf(-2.f, s.z, q.z); d[3] = fmaf(-2.f, s.w, q.w);
       }
       // candidates of this group of 128 entries: bit (4 * lane + e) of a 128-bit set, walked in index order
@@ -168,7 +184,7 @@ static int grid_for(long long work_blocks, int per_sm) {
   return static_cast<int>(g > 0 ? g : 1);
 }
 
-int launch_rvq_select(const float* scores, const float* e_sq, const float* codebook, float* resid, void* resid16,
+int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, const float* codebook, float* resid, void* resid16,
                       long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
                       cudaStream_t st) {
   if (rows < 0 || n_codes <= 0 || n_codes % 4 != 0 || !(e_max >= 0.f) || !(tau_rel >= 0.f)) return -1;
@@ -179,8 +195,12 @@ int launch_rvq_select(const float* scores, const float* e_sq, const float* codeb
        reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(resid16)) & 15u)
     return -3;
   const int grid = grid_for((rows + rvq::kWarps - 1) / rvq::kWarps, 8);
-  rvq_select_kernel<<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16), codes,
-                                                      n_candidates, rows, n_codes, e_max, tau_rel);
+  if (scores_fp16)
+    rvq_select_kernel<true><<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16),
+                                                              codes, n_candidates, rows, n_codes, e_max, tau_rel);
+  else
+    rvq_select_kernel<false><<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16),
+                                                               codes, n_candidates, rows, n_codes, e_max, tau_rel);
   return static_cast<int>(cudaGetLastError());
 }
 

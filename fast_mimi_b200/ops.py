@@ -402,7 +402,7 @@ def rope_fp32_(t, cos, sin):
 
 # --------------------------------------------------------------------------- residual vector quantisation
 RVQ_DIM = 256
-RVQ_TAU_REL = 4.5e-3     # covers the FP16 rounding of both operands of the pre-selecting inner products
+RVQ_TAU_REL = {torch.float32: 4.5e-3, torch.float16: 5.5e-3}   # FP16 rounding of both operands (+ of the stored scores)
 
 
 class RVQCodebooks:
@@ -421,11 +421,13 @@ class RVQCodebooks:
         self.layers, self.entries = codebooks.shape[0], codebooks.shape[1]
 
 
-def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates=False, status=None):
+def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates=False, scores_dtype=torch.float16,
+               status=None):
     """Codes ``[layers, rows]`` int64 of the residual quantiser stack for ``x [rows, 256]`` float32 (the output
     of the branch's ``input_proj``).  Per layer: inner products with all entries on the tensor core (FP16
     operands) pre-select, the exact FP32 distance decides among the candidates, the chosen entry is subtracted.
-    ``x`` is not modified."""
+    The scores make one round trip through memory, in FP16 by default (half the traffic; the candidate margin
+    accounts for their rounding).  ``x`` is not modified."""
     lib = _native.load()
     _need(x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] == RVQ_DIM, "x must be CUDA float32 [rows, 256]")
     layers = books.layers if num_quantizers is None else int(num_quantizers)
@@ -433,15 +435,16 @@ def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates
     rows = x.shape[0]
     resid = x.contiguous().clone()
     resid16 = torch.empty(rows, RVQ_DIM, dtype=torch.float16, device=x.device)
-    scores = torch.empty(rows, books.entries, dtype=torch.float32, device=x.device)
+    _need(scores_dtype in RVQ_TAU_REL, "scores_dtype must be float16 or float32")
+    scores = torch.empty(rows, books.entries, dtype=scores_dtype, device=x.device)
     codes = torch.empty(layers, rows, dtype=torch.int64, device=x.device)
     cand = torch.empty(layers, rows, dtype=torch.int32, device=x.device) if return_candidates else None
     _native.check(lib.fm_rvq_to_half(resid.data_ptr(), resid16.data_ptr(), rows, _stream()), "fm_rvq_to_half")
     for l in range(layers):
-        linear(resid16, books.half[l], out_dtype=torch.float32, out=scores, status=status)
-        rc = lib.fm_rvq_select_f32(scores.data_ptr(), books.sq[l].data_ptr(), books.vectors[l].data_ptr(), resid.data_ptr(),
+        linear(resid16, books.half[l], out_dtype=scores_dtype, out=scores, status=status)
+        rc = lib.fm_rvq_select_f32(scores.data_ptr(), _OUT_CODES[scores_dtype], books.sq[l].data_ptr(), books.vectors[l].data_ptr(), resid.data_ptr(),
                                    resid16.data_ptr(), codes[l].data_ptr(), cand[l].data_ptr() if cand is not None else None,
-                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL, _stream())
+                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL[scores_dtype], _stream())
         _native.check(rc, "fm_rvq_select_f32")
     return (codes, cand) if return_candidates else codes
 

@@ -80,18 +80,19 @@ int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const floa
 /* One layer of residual vector quantisation for `rows` frames of 256 dimensions against a codebook of n_codes
  * entries: replaces MimiEuclideanCodebook.quantize (argmin over torch.cdist, src/fast_mimi/model.py:2277-2291) and
  * the residual update of MimiResidualVectorQuantizer.encode (src/fast_mimi/model.py:2420-2427).
- *   scores    [rows, n_codes] FP32: inner products residual . e_j computed from FP16 copies of both (fm_linear_f16
- *             with a = residual16, w = FP16 codebook, FP32 output); they pre-select only
+ *   scores    [rows, n_codes], scores_dtype 1 = FP16 or 2 = FP32 (the out_dtype codes of fm_linear_f16): inner
+ *             products residual . e_j computed from FP16 copies of both (fm_linear_f16 with a = residual16,
+ *             w = FP16 codebook); they pre-select only
  *   e_sq      [n_codes] FP32: |e_j|^2      codebook [n_codes, 256] FP32      e_max = max_j |e_j|
  *   residual  [rows, 256] FP32, in/out: the chosen entry is subtracted
  *   residual16 [rows, 256] FP16 out: copy of the new residual for the next layer's inner products
  *   codes     [rows] int64 out        n_candidates [rows] int32 out or NULL (entries that were decided exactly)
  * Every entry whose approximate distance is within tau_rel * |residual| * e_max of the minimum is re-evaluated as
  * sum_k (x_k - e_jk)^2 in FP32; the smallest wins, the lowest index on ties.  tau_rel = 4.5e-3 covers the FP16
- * operand rounding. */
-int fm_rvq_select_f32(const float* scores, const float* e_sq, const float* codebook, float* residual,
-                      void* residual16, long long* codes, int* n_candidates, long long rows, int n_codes,
-                      float e_max, float tau_rel, void* stream);
+ * operand rounding with FP32 scores, 5.5e-3 with FP16 scores. */
+int fm_rvq_select_f32(const void* scores, int scores_dtype, const float* e_sq, const float* codebook,
+                      float* residual, void* residual16, long long* codes, int* n_candidates, long long rows,
+                      int n_codes, float e_max, float tau_rel, void* stream);
 
 /* FP16 copy of [rows, 256] FP32 values (the residual before the first layer). */
 int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream);

@@ -31,8 +31,9 @@ def test_rvq_codes_match_the_reference_fixture():
     assert torch.equal(dec[:, :, ::13], g["quantized_probe"])             # ordered FP32 adds: bit-exact
 
 
+@pytest.mark.parametrize("scores_dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("rows,layers", [(1, 8), (257, 3), (6000, 8)])
-def test_rvq_codes_match_the_oracle(rows, layers):
+def test_rvq_codes_match_the_oracle(rows, layers, scores_dtype):
     """Frame-level identity (all layers' codes equal) against the CPU oracle; inputs scaled so that the later
     layers see residuals two orders of magnitude smaller than the first."""
     import fast_mimi_b200 as fm
@@ -42,7 +43,7 @@ def test_rvq_codes_match_the_oracle(rows, layers):
     x = torch.randn(rows, 256, generator=gen) * 1.5
     want = O.rvq_encode(x, books)
     gb = fm.ops.RVQCodebooks(books.cuda())
-    got = fm.ops.rvq_encode(x.cuda(), gb).cpu()
+    got = fm.ops.rvq_encode(x.cuda(), gb, scores_dtype=scores_dtype).cpu()
     same = (got == want).all(dim=0).float().mean()
     assert same >= 0.995, float(same)
     assert torch.equal(fm.ops.rvq_decode(got.cuda(), gb).cpu(), O.rvq_decode(got, books))
