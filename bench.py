@@ -451,7 +451,7 @@ def profile_case(which: str) -> None:
     a handful of launches): prefill = 256 clips x 250 frames, one layer; decode = 512 streams on a
     full ring, one layer; layer = one whole transformer layer on 256 clips x 250 frames (LayerNorm and the
     three epilogue variants of the linear kernel); longclip = 16 clips x 2500 frames, three input sets in
-    rotation.  Prints nothing that is a benchmark value."""
+    rotation; rvq = 64 000 vectors through two quantiser layers.  Prints nothing that is a benchmark value."""
     import fast_mimi_b200 as fm
     from fast_mimi_b200 import ops
     dev = torch.device("cuda", 0)
@@ -470,6 +470,11 @@ def profile_case(which: str) -> None:
         with torch.no_grad():
             for _ in range(3):
                 layer(x, None, None, (cos, sin), False)
+    elif which == "rvq":
+        books = ops.RVQCodebooks(torch.randn(2, 2048, 256, device=dev, generator=g))
+        xq = torch.randn(64000, 256, device=dev, generator=g) * 1.5
+        for _ in range(2):
+            ops.rvq_encode(xq, books)
     elif which == "longclip":
         sets = [tuple((torch.randn(16, 2500, HIDDEN, device=dev, generator=g) / 8).to(dt)
                       for dt in (torch.bfloat16, torch.bfloat16, torch.float16)) for _ in range(3)]
@@ -691,7 +696,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
-    ap.add_argument("--profile-case", choices=["prefill", "decode", "layer", "longclip"], help="run a small case for ncu and exit")
+    ap.add_argument("--profile-case", choices=["prefill", "decode", "layer", "longclip", "rvq"], help="run a small case for ncu and exit")
     ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "stack", "rvq"],
                     help="prefill = headline (config 3); longclip / stream = configs 4 / 5, stack = whole transformer layers, rvq = the quantiser after the encoder transformer; one extra JSON line each")
     args = ap.parse_args()

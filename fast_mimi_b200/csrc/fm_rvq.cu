@@ -23,6 +23,7 @@ namespace fm {
 namespace rvq {
 constexpr int kDim = 256;        // codebook dimension
 constexpr int kWarps = 8;        // warps (frames in flight) per block
+constexpr int kMaxIters = 16;    // a lane keeps 4 * kMaxIters approximate distances: up to 2048 entries per codebook
 }  // namespace rvq
 
 namespace rvq {
@@ -46,6 +47,7 @@ rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_s
                   int* __restrict__ n_candidates, long long rows, int n_codes, float e_max, float tau_rel) {
   using namespace rvq;
   const int lane = threadIdx.x & 31;
+  const int n_iters = n_codes >> 7;
   const long long warp0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   const long long stride = static_cast<long long>(gridDim.x) * kWarps;
   for (long long row = warp0; row < rows; row += stride) {
@@ -64,56 +66,62 @@ rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_s
     // relative part: FP16 rounding of both operands; absolute part: residual values below FP16's normal range
     const float tau = tau_rel * sqrtf(xx) * e_max + 3.1e-5f * e_max;
 
-    // pass A: minimum of the approximate distances
+    // pass A: approximate distances of this lane's entries (kept in registers) and their minimum.  Lane l holds
+    // entries 128 * it + 4 * l + e, it = 0 .. n_codes / 128 - 1, e = 0 .. 3.
     const void* s4 = static_cast<const uint8_t*>(scores) + static_cast<size_t>(row) * n_codes * (kHalf ? 2 : 4);
     const float4* q4 = reinterpret_cast<const float4*>(e_sq);
-    const int n_vec = n_codes >> 2;                  // float4 groups per row
+    float d[kMaxIters][4];
     float d_min = INFINITY;
-    for (int v = lane; v < n_vec; v += 32) {
-      const float4 s = load_scores4<kHalf>(s4, v), q = __ldg(q4 + v);
-      d_min = fminf(d_min, fminf(fminf(fmaf(-2.f, s.x, q.x), fmaf(-2.f, s.y, q.y)),
-                                 fminf(fmaf(-2.f, s.z, q.z), fmaf(-2.f, s.w, q.w))));
+#pragma unroll
+    for (int it = 0; it < kMaxIters; ++it) {
+      if (it < n_iters) {                            // the same for every lane
+        const float4 s = load_scores4<kHalf>(s4, it * 32 + lane), q = __ldg(q4 + it * 32 + lane);
+        d[it][0] = fmaf(-2.f, s.x, q.x); d[it][1] = fmaf(-2.f, s.y, q.y);
+        d[it][2] = fmaf(-2.f, s.z, q.z); d[it][3] = fmaf(-2.f, s.w, q.w);
+        d_min = fminf(d_min, fminf(fminf(d[it][0], d[it][1]), fminf(d[it][2], d[it][3])));
+      } else {
+        d[it][0] = d[it][1] = d[it][2] = d[it][3] = INFINITY;
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) d_min = fminf(d_min, __shfl_xor_sync(0xffffffffu, d_min, o));
     const float limit = d_min + tau;
 
-    // pass B: exact distance of every candidate, in ascending index order
+    // pass B: every lane marks its candidates (bit 4 * it + e); the warp then evaluates them one by one exactly
+    unsigned long long mine = 0ull;
+#pragma unroll
+    for (int it = 0; it < kMaxIters; ++it) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (d[it][e] <= limit) mine |= 1ull << (4 * it + e);
+    }
     float best = INFINITY;
     int best_j = 0, n_cand = 0;
-    for (int v0 = 0; v0 < n_vec; v0 += 32) {
-      const int v = v0 + lane;
-      float d[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
-      if (v < n_vec) {
-        const float4 s = load_scores4<kHalf>(s4, v), q = __ldg(q4 + v);
-        d[0] = fmaf(-2.f, s.x, q.x); d[1] = fmaf(-2.f, s.y, q.y); d[2] = fmaf(-2.f, s.z, q.z); d[3] = fmaf(-2.f, s.w, q.w);
-      }
-      // candidates of this group of 128 entries: bit (4 * lane + e) of a 128-bit set, walked in index order
+    unsigned lanes = __ballot_sync(0xffffffffu, mine != 0ull);
+    while (lanes != 0u) {
+      const int src = __ffs(lanes) - 1;
+      lanes &= lanes - 1u;
+      unsigned long long bits = __shfl_sync(0xffffffffu, mine, src);
+      while (bits != 0ull) {
+        const int bit = __ffsll(static_cast<long long>(bits)) - 1;
+        bits &= bits - 1ull;
+        const int j = (bit >> 2) * 128 + src * 4 + (bit & 3);
+        const float4* er = reinterpret_cast<const float4*>(codebook + static_cast<size_t>(j) * kDim + lane * 8);
+        const float4 a = __ldg(er), b = __ldg(er + 1);
+        const float ev[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        float acc = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        unsigned mask = __ballot_sync(0xffffffffu, d[e] <= limit);
-        while (mask != 0u) {
-          const int src = __ffs(mask) - 1;
-          mask &= mask - 1u;
-          const int j = (v0 + src) * 4 + e;
-          const float4* er = reinterpret_cast<const float4*>(codebook + static_cast<size_t>(j) * kDim + lane * 8);
-          const float4 a = __ldg(er), b = __ldg(er + 1);
-          const float ev[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-          float acc = 0.f;
+        for (int k = 0; k < 8; ++k) {
+          const float t = x[k] - ev[k];
+          acc = fmaf(t, t, acc);
+        }
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const float t = x[k] - ev[k];
-            acc = fmaf(t, t, acc);
-          }
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-          ++n_cand;
-          // Within one (e) sweep indices ascend with the lane; across the four sweeps of a group they interleave,
-          // so ties are resolved explicitly in favour of the lower index.
-          if (acc < best || (acc == best && j < best_j)) {
-            best = acc;
-            best_j = j;
-          }
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        ++n_cand;
+        // candidates do not come in index order: ties go to the lower index explicitly (argmin's rule)
+        if (acc < best || (acc == best && j < best_j)) {
+          best = acc;
+          best_j = j;
         }
       }
     }
@@ -187,7 +195,9 @@ static int grid_for(long long work_blocks, int per_sm) {
 int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, const float* codebook, float* resid, void* resid16,
                       long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
                       cudaStream_t st) {
-  if (rows < 0 || n_codes <= 0 || n_codes % 4 != 0 || !(e_max >= 0.f) || !(tau_rel >= 0.f)) return -1;
+  if (rows < 0 || n_codes <= 0 || n_codes % 128 != 0 || n_codes > 128 * rvq::kMaxIters || !(e_max >= 0.f) ||
+      !(tau_rel >= 0.f))
+    return -1;
   if (rows == 0) return 0;
   if (scores == nullptr || e_sq == nullptr || codebook == nullptr || resid == nullptr || resid16 == nullptr || codes == nullptr)
     return -1;

@@ -412,8 +412,8 @@ class RVQCodebooks:
 
     def __init__(self, codebooks: torch.Tensor) -> None:
         _need(codebooks.is_cuda and codebooks.dtype == torch.float32 and codebooks.dim() == 3
-              and codebooks.shape[2] == RVQ_DIM and codebooks.shape[1] % 256 == 0,
-              "codebooks must be CUDA float32 [layers, entries (multiple of 256), 256]")
+              and codebooks.shape[2] == RVQ_DIM and codebooks.shape[1] % 256 == 0 and codebooks.shape[1] <= 2048,
+              "codebooks must be CUDA float32 [layers, entries (multiple of 256, at most 2048), 256]")
         self.vectors = codebooks.contiguous()
         self.half = self.vectors.half().contiguous()
         self.sq = (self.vectors.double() ** 2).sum(-1).float().contiguous()           # [layers, entries]
