@@ -14,8 +14,9 @@
 // 256 weight rows, each CTA contributing half of the weight tile.  Accumulators: two 256-column TMEM buffers
 // per CTA, so the epilogue of one unit overlaps the MMAs of the next.  Persistent: (row-tile pair, 256-wide
 // output tile) units, numbered row-tile-major, are dealt round-robin to the pairs, so the output tiles of a
-// row tile are computed at the same time by neighbouring pairs and share its a slices through L2.  Warps 0-7: epilogue (two per TMEM lane group, two 64-column
-// groups each).  Warp 8: TMA producer (+ TMEM allocation).  Warp 9: MMA issuer (leader CTA only).
+// row tile are computed at the same time by neighbouring pairs and share its a slices through L2.
+// Warps 0-7: epilogue (two per TMEM lane group, two 64-column groups each).  Warp 8: TMA producer (+ TMEM
+// allocation).  Warp 9: MMA issuer (leader CTA only).
 #include <type_traits>
 
 #include "fm_common.cuh"

@@ -9,9 +9,9 @@
 // Search: the 2048 inner products per frame are a GEMM and run on the tensor core with FP16 operands (the general
 // linear kernel of this library, K = 256, N = 2048).  They only PRE-SELECT: for a frame x the approximate
 // distances  |e_j|^2 - 2 x.e_j  differ from the exact ones by at most  tau = tau_rel * |x| * max_j |e_j|
-// (operand rounding 2^-11 each, FP32 accumulation, plus another 2^-11 when the scores are stored as FP16), so every
-// entry within tau of the approximate minimum is a
-// candidate and the entry that wins is decided among the candidates by the exact FP32 distance
+// (operand rounding 2^-11 each, FP32 accumulation, plus another 2^-11 when the scores are stored as FP16), so
+// every entry within tau of the approximate minimum is a candidate and the entry that wins is decided among the
+// candidates by the exact FP32 distance
 // sum_k (x_k - e_jk)^2, lowest index on ties (argmin's rule).  rvq_select_kernel does that per frame with one
 // warp, writes the code, subtracts the entry from the residual (FP32, in place) and emits the FP16 copy of the
 // new residual that the next layer's GEMM consumes.
@@ -24,9 +24,7 @@ namespace rvq {
 constexpr int kDim = 256;        // codebook dimension
 constexpr int kWarps = 8;        // warps (frames in flight) per block
 constexpr int kMaxIters = 16;    // a lane keeps 4 * kMaxIters approximate distances: up to 2048 entries per codebook
-}  // namespace rvq
 
-namespace rvq {
 // Four consecutive scores of a row, stored as FP32 or as FP16.
 template <bool kHalf>
 __device__ __forceinline__ float4 load_scores4(const void* row_base, int v) {
