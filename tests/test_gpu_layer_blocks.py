@@ -115,3 +115,38 @@ def test_transformer_layer_shares_parameters_with_the_module_it_replaces():
     new = fm.MimiTransformerLayerB200.from_reference(src)
     assert new.mlp.fc1.weight is src.mlp.fc1.weight and new.self_attn.q_proj.weight is src.self_attn.q_proj.weight
     assert sorted(new.state_dict()) == sorted(src.state_dict())
+
+
+def test_install_layers_replaces_every_layer_and_keeps_the_numbers():
+    """install_layers on a module with a `layers` ModuleList (the reference's MimiTransformerModel attribute):
+    every entry becomes a MimiTransformerLayerB200 that shares the parameters, so a two-layer pass gives the same
+    result as before and matches the oracle."""
+    import torch.nn as nn
+    import fast_mimi_b200 as fm
+    stack = nn.Module()
+    stack.layers = nn.ModuleList([fm.MimiTransformerLayerB200(layer_idx=i) for i in range(2)])
+    params = [_layer_params(50 + i) for i in range(2)]
+    for layer, p in zip(stack.layers, params):
+        layer.load_state_dict(p, strict=True)
+    stack = stack.cuda()
+    T = 200
+    x = torch.randn(2, T, 512, generator=torch.Generator().manual_seed(52))
+    cos, sin = O.rope_tables(torch.arange(T))
+    pe = (cos.cuda()[None], sin.cuda()[None])
+
+    def run(mod):
+        h = x.cuda()
+        for layer in mod.layers:
+            h, _ = layer(h, None, None, pe, False)
+        return h.cpu()
+
+    before = run(stack)
+    old_weight = stack.layers[1].mlp.fc2.weight
+    fm.install_layers(stack)
+    assert all(isinstance(l, fm.MimiTransformerLayerB200) for l in stack.layers)
+    assert stack.layers[1].mlp.fc2.weight is old_weight
+    assert torch.equal(run(stack), before)
+    ref = x
+    for p in params:
+        ref = O.transformer_layer(ref, p)
+    assert O.rel_l2(before - x, ref - x) < 2e-3
