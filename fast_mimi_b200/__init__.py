@@ -9,8 +9,10 @@ Public surface:
   MimiSplitRVQB200         encode / decode of the reference's split residual vector quantiser
   MimiKVRing               streaming KV state with ``MimiKVCache``'s bookkeeping interface
   ops                      tensor-level wrappers over the C ABI (include/fast_mimi_b200.h)
+  check_status             synchronise and raise if a kernel recorded an error in the device status word
 """
 from . import ops
+from .ops import check_status
 from .attention import (MimiAttentionB200, install, native_window_attention, rope_tables, window_attention_fp32,
                         window_attention_nlc)
 from .kv_ring import LinearKVCache, MimiKVRing
@@ -19,4 +21,4 @@ from .rvq import MimiRVQB200, MimiSplitRVQB200
 from .sharding import gather_to_host, shard, shard_bounds
 
 __all__ = ["MimiAttentionB200", "MimiTransformerLayerB200", "install_layers", "MimiRVQB200", "MimiSplitRVQB200", "MimiKVRing", "LinearKVCache", "install", "native_window_attention",
-           "window_attention_fp32", "window_attention_nlc", "rope_tables", "ops", "shard", "shard_bounds", "gather_to_host"]
+           "window_attention_fp32", "window_attention_nlc", "rope_tables", "ops", "check_status", "shard", "shard_bounds", "gather_to_host"]

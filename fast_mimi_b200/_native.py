@@ -14,14 +14,14 @@ from ._build import LIB_PATH
 
 _P, _I, _LL, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
-#: name -> argtypes, in header order.  tests/test_abi_symbols.py checks this table against the header.
+#: name -> argtypes, in header order.  tests/test_host_logic.py checks this table against the header.
 SIGNATURES: dict[str, list] = {
     "fm_abi_version": [],
     "fm_qkv_rope_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _I, _I, _I, _P, _P],
     "fm_out_proj_f16": [_P, _P, _P, _P, _P, _LL, _I, _P, _P],
     "fm_linear_f16": [_P, _P, _P, _P, _P, _LL, _I, _I, _I, _I, _I, _P, _P],
     "fm_layernorm_f16": [_P, _I, _P, _P, _F, _P, _I, _LL, _P],
-    "fm_rvq_select_f32": [_P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _F, _F, _P],
+    "fm_rvq_select_f32": [_P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _F, _F, _P, _P],
     "fm_rvq_to_half": [_P, _P, _LL, _P],
     "fm_rvq_decode_f32": [_P, _P, _P, _LL, _I, _I, _P, _P],
     "fm_band_attn_prefill_bf16": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],

@@ -65,7 +65,7 @@ using fm::QkvEpilogueArgs;
 
 extern "C" {
 
-int fm_abi_version(void) { return 1; }
+int fm_abi_version(void) { return 2; }
 
 int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                      void* q, void* k, void* v, int B, int T, int value_dtype, int* status, void* stream) {
@@ -119,10 +119,10 @@ int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const floa
 
 int fm_rvq_select_f32(const void* scores, int scores_dtype, const float* e_sq, const float* codebook, float* residual,
                       void* residual16, long long* codes, int* n_candidates, long long rows, int n_codes, float e_max,
-                      float tau_rel, void* stream) {
+                      float tau_rel, int* status, void* stream) {
   if (scores_dtype != 1 && scores_dtype != 2) return -1;
   return fm::launch_rvq_select(scores, scores_dtype == 1, e_sq, codebook, residual, residual16, codes, n_candidates, rows, n_codes, e_max,
-                               tau_rel, static_cast<cudaStream_t>(stream));
+                               tau_rel, status, static_cast<cudaStream_t>(stream));
 }
 
 int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream) {
@@ -145,7 +145,7 @@ int fm_ring_attn_decode_bf16(const void* q, const void* ring_k, const void* ring
 int fm_decode_step_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                         const int* stream_pos, int pos_base, void* q_ws, void* ring_k, void* ring_v, float* out,
                         int S, int ring_slots, float scale, int value_dtype, int* status, void* stream) {
-  if (S < 0 || value_dtype < 0 || value_dtype > 3 || ring_slots <= 0 || ring_slots > 256) return -1;
+  if (S < 0 || value_dtype < 0 || value_dtype > 3 || ring_slots <= 0 || ring_slots > 256 || pos_base < 0) return -1;
   if (ring_k == nullptr || ring_v == nullptr || q_ws == nullptr) return -1;
   QkvEpilogueArgs ep = {};
   ep.q = static_cast<uint16_t*>(q_ws);

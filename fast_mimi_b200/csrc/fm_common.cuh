@@ -22,6 +22,7 @@ enum Status : int {
   kErrWaitMma = 102,       // a tcgen05.commit barrier never flipped
   kErrWaitConsumer = 103,  // a consumer->producer "slot free" barrier never flipped
   kErrBounds = 104,        // a self-check found an out-of-range index
+  kErrNonFinite = 105,     // an input that must be finite was not (no decision could be made from it)
 };
 
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s

@@ -140,10 +140,17 @@ ring_decode_attn_kernel(const uint16_t* __restrict__ q, const uint16_t* __restri
   __syncthreads();
   CtaCtl* ctl = &c->ctl;
 
+  // Slots 0..pos while the ring fills, all of them once it has wrapped.  A negative position (a caller
+  // error that only a device-side stream_pos can still carry past the host checks) is recorded as
+  // kErrBounds and the item reads slot 0 only, so no copy size or address is ever derived from it.
   auto valid_slots = [&](int item) {
     const int s = item >> 3;
     const int pos = pos_base + (stream_pos != nullptr ? stream_pos[s] : 0);
-    return pos + 1 < ring_slots ? pos + 1 : ring_slots;   // slots 0..pos while filling, all once wrapped
+    if (pos < 0) {
+      if (status != nullptr) atomicMax(status, static_cast<int>(kErrBounds));
+      return 1;
+    }
+    return pos + 1 < ring_slots ? pos + 1 : ring_slots;
   };
 
   if (warp == kGroups * kWarps) {
@@ -332,7 +339,7 @@ int launch_ring_decode_attn(const void* q, const void* ring_k, const void* ring_
                             int value_is_fp16, int* status, cudaStream_t st) {
   using namespace dec;
   if (S <= 0) return S == 0 ? 0 : -1;
-  if (ring_slots <= 0 || ring_slots > kMaxSlots || S > (1 << 27)) return -1;
+  if (ring_slots <= 0 || ring_slots > kMaxSlots || S > (1 << 27) || pos_base < 0) return -1;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(ring_k) | reinterpret_cast<uintptr_t>(ring_v)) & 15u)
     return -3;
   int dev = 0, sms = 0;

@@ -61,7 +61,7 @@ int launch_layernorm512(const void* x, int x_dtype, const float* weight, const f
 // the residual, ordered FP32 decode.
 int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, const float* codebook, float* resid, void* resid16,
                       long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
-                      cudaStream_t st);
+                      int* status, cudaStream_t st);
 int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st);
 int launch_rvq_decode(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
                       int n_codes, int* bad_code, cudaStream_t st);

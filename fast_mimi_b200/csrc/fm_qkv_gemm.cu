@@ -223,8 +223,13 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
         ring_row = -1;
         if (ep.ring_k != nullptr && row_ok) {
           const int pos = ep.pos_base + (ep.clip_pos != nullptr ? ep.clip_pos[clip] : 0) + t;
-          // Only the newest ring_slots frames of a clip land in the ring.
-          if (t >= ep.T - ep.ring_slots) ring_row = static_cast<long long>(clip) * 8 * ep.ring_slots + pos % ep.ring_slots;
+          // Only the newest ring_slots frames of a clip land in the ring.  A negative position would index
+          // another stream's ring: it is recorded and the write is dropped.
+          if (pos < 0) {
+            if (status != nullptr) atomicMax(status, static_cast<int>(kErrBounds));
+          } else if (t >= ep.T - ep.ring_slots) {
+            ring_row = static_cast<long long>(clip) * 8 * ep.ring_slots + pos % ep.ring_slots;
+          }
         }
       }
       const int buf = i & 1;

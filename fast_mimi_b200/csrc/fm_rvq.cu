@@ -9,12 +9,18 @@
 // Search: the 2048 inner products per frame are a GEMM and run on the tensor core with FP16 operands (the general
 // linear kernel of this library, K = 256, N = 2048).  They only PRE-SELECT: for a frame x the approximate
 // distances  |e_j|^2 - 2 x.e_j  differ from the exact ones by at most  tau = tau_rel * |x| * max_j |e_j|
-// (operand rounding 2^-11 each, FP32 accumulation, plus another 2^-11 when the scores are stored as FP16), so
+// (see the derivation of tau_rel below), so
 // every entry within tau of the approximate minimum is a candidate and the entry that wins is decided among the
 // candidates by the exact FP32 distance
 // sum_k (x_k - e_jk)^2, lowest index on ties (argmin's rule).  rvq_select_kernel does that per frame with one
 // warp, writes the code, subtracts the entry from the residual (FP32, in place) and emits the FP16 copy of the
 // new residual that the next layer's GEMM consumes.
+//
+// tau_rel: rounding x and e to FP16 perturbs x.e by at most 2 * 2^-11 |x||e| (to first order), storing the score as
+// FP16 by another 2^-11 |x||e|, so d_j = |e_j|^2 - 2 x.e_j is off by at most 4 * 2^-11 |x||e| = 1.95e-3 |x||e| with
+// FP32 scores and 6 * 2^-11 |x||e| = 2.93e-3 |x||e| with FP16 scores.  The true winner's d may be too high and the
+// approximate minimum too low by that much each, so the candidate margin must be twice the bound: 3.9e-3 and
+// 5.86e-3.  Callers pass 4.5e-3 / 6.0e-3.
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -42,7 +48,8 @@ template <bool kHalf>
 __global__ void __launch_bounds__(rvq::kWarps * 32)
 rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_sq, const float* __restrict__ codebook,
                   float* __restrict__ resid, uint16_t* __restrict__ resid16, long long* __restrict__ codes,
-                  int* __restrict__ n_candidates, long long rows, int n_codes, float e_max, float tau_rel) {
+                  int* __restrict__ n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
+                  int* __restrict__ status) {
   using namespace rvq;
   const int lane = threadIdx.x & 31;
   const int n_iters = n_codes >> 7;
@@ -141,6 +148,9 @@ rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_s
     if (lane == 0) {
       codes[row] = best_j;
       if (n_candidates != nullptr) n_candidates[row] = n_cand;
+      // A residual that is not finite (or overflows FP16) makes every approximate distance NaN: nothing was a
+      // candidate and the code above is meaningless.  Say so instead of emitting entry 0 silently.
+      if (n_cand == 0 && status != nullptr) atomicMax(status, static_cast<int>(kErrNonFinite));
     }
   }
 }
@@ -192,7 +202,7 @@ static int grid_for(long long work_blocks, int per_sm) {
 
 int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, const float* codebook, float* resid, void* resid16,
                       long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
-                      cudaStream_t st) {
+                      int* status, cudaStream_t st) {
   if (rows < 0 || n_codes <= 0 || n_codes % 128 != 0 || n_codes > 128 * rvq::kMaxIters || !(e_max >= 0.f) ||
       !(tau_rel >= 0.f))
     return -1;
@@ -205,10 +215,10 @@ int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, co
   const int grid = grid_for((rows + rvq::kWarps - 1) / rvq::kWarps, 8);
   if (scores_fp16)
     rvq_select_kernel<true><<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16),
-                                                              codes, n_candidates, rows, n_codes, e_max, tau_rel);
+                                                              codes, n_candidates, rows, n_codes, e_max, tau_rel, status);
   else
     rvq_select_kernel<false><<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16),
-                                                               codes, n_candidates, rows, n_codes, e_max, tau_rel);
+                                                               codes, n_candidates, rows, n_codes, e_max, tau_rel, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -87,6 +87,25 @@ def read_status(status: torch.Tensor) -> int:
     return _native.load().fm_read_status(status.data_ptr(), _stream())
 
 
+STATUS_NAMES = {101: "a TMA completion barrier never flipped", 102: "a tensor-core completion barrier never flipped",
+                103: "a consumer never released a buffer", 104: "a device-side bounds check failed "
+                "(for instance a negative stream position)",
+                105: "an input that must be finite was not (no quantiser entry could be chosen)"}
+
+
+def check_status(device=None, status: torch.Tensor | None = None) -> None:
+    """Synchronise the current stream and raise ``RuntimeError`` if a kernel recorded an error in the status
+    word (``status``, or the device's default word).  The word is sticky: once it is non-zero every later
+    kernel handed the same word returns without doing its work, so results produced since the last check
+    must be discarded; clear it with ``.zero_()`` after handling the error.  The kernels never synchronise,
+    so callers of the attention / layer modules call this at their own synchronisation points."""
+    st = default_status(device if device is not None else torch.cuda.current_device()) if status is None else status
+    code = read_status(st)
+    if code != 0:
+        raise RuntimeError(f"fast_mimi_b200: device status {code} ({STATUS_NAMES.get(code, 'unknown code')}); "
+                           "outputs written since the last check are not valid; clear the word with .zero_()")
+
+
 def qkv_rope(x, w_qkv, cos, sin, *, value_dtype=torch.float16, out=None, status=None):
     """``x [B,T,512] bf16`` -> rotated ``q, k`` (bf16) and ``v`` (value_dtype), each ``[B,T,512]``."""
     lib = _native.load()
@@ -272,6 +291,7 @@ def decode_step(x, w_qkv, cos, sin, ring_k, ring_v, position, *, scale=0.125, q_
     stream s has absolute position ``position + stream_pos[s]``.  Returns ``[S,512] float32``."""
     lib = _native.load()
     _need(x.dim() == 2, "x must be [S, 512]")
+    _need(int(position) >= 0, "position must not be negative")
     S = x.shape[0]
     in_flag = _check_projection_inputs(x, w_qkv)
     bstride = 0 if cos.shape[0] == 1 else HEAD_DIM
@@ -331,6 +351,8 @@ class DecodePlan:
 
     def step(self, position: int, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         """``cos, sin``: contiguous float32 ``[1, 1, 64]`` tables of the new frame's position."""
+        if position < 0:
+            raise RuntimeError("unexpected attention geometry: position must not be negative")
         rc = self._lib.fm_decode_step_bf16(*self._args_head, cos.data_ptr(), sin.data_ptr(), 0, None, int(position),
                                            *self._args_tail, _stream())
         if rc != 0:
@@ -402,7 +424,9 @@ def rope_fp32_(t, cos, sin):
 
 # --------------------------------------------------------------------------- residual vector quantisation
 RVQ_DIM = 256
-RVQ_TAU_REL = {torch.float32: 4.5e-3, torch.float16: 5.5e-3}   # FP16 rounding of both operands (+ of the stored scores)
+# Candidate margins relative to |x| * max|e|: twice the worst-case error of an approximate distance, which is
+# 4 * 2^-11 (FP16 rounding of both operands) with FP32 scores and 6 * 2^-11 with FP16-stored scores.
+RVQ_TAU_REL = {torch.float32: 4.5e-3, torch.float16: 6.0e-3}
 
 
 class RVQCodebooks:
@@ -444,7 +468,8 @@ def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates
         linear(resid16, books.half[l], out_dtype=scores_dtype, out=scores, status=status)
         rc = lib.fm_rvq_select_f32(scores.data_ptr(), _OUT_CODES[scores_dtype], books.sq[l].data_ptr(), books.vectors[l].data_ptr(), resid.data_ptr(),
                                    resid16.data_ptr(), codes[l].data_ptr(), cand[l].data_ptr() if cand is not None else None,
-                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL[scores_dtype], _stream())
+                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL[scores_dtype], _status_ptr(status, x),
+                                   _stream())
         _native.check(rc, "fm_rvq_select_f32")
     return (codes, cand) if return_candidates else codes
 
@@ -464,4 +489,5 @@ def rvq_decode(codes, books: RVQCodebooks):
     _native.check(rc, "fm_rvq_decode_f32")
     if int(bad.item()) != 0:
         raise RuntimeError("rvq_decode: a code index is outside the codebook")
+    check_status(codes.device)      # the stream is already synchronised by the read above
     return out

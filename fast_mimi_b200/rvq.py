@@ -37,6 +37,9 @@ class MimiRVQB200:
         if self.input_proj is not None:
             x = ops.linear_fp32(x.contiguous(), self.input_proj)
         codes = ops.rvq_encode(x.contiguous(), self.books, num_quantizers)
+        # codes are the end of the device pipeline: a recorded error (a timed-out wait in a kernel upstream, a
+        # non-finite residual) must not leave as plausible-looking indices
+        ops.check_status(embeddings.device)
         return codes.view(codes.shape[0], B, T)
 
     def decode(self, codes: torch.Tensor) -> torch.Tensor:

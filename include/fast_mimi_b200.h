@@ -89,10 +89,11 @@ int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const floa
  *   codes     [rows] int64 out        n_candidates [rows] int32 out or NULL (entries that were decided exactly)
  * Every entry whose approximate distance is within tau_rel * |residual| * e_max of the minimum is re-evaluated as
  * sum_k (x_k - e_jk)^2 in FP32; the smallest wins, the lowest index on ties.  tau_rel = 4.5e-3 covers the FP16
- * operand rounding with FP32 scores, 5.5e-3 with FP16 scores. */
+ * operand rounding with FP32 scores, 6.0e-3 with FP16 scores (twice the worst-case error of a distance).
+ * A frame whose residual is not finite has no candidate: code 105 is recorded in *status (NULL = not recorded). */
 int fm_rvq_select_f32(const void* scores, int scores_dtype, const float* e_sq, const float* codebook,
                       float* residual, void* residual16, long long* codes, int* n_candidates, long long rows,
-                      int n_codes, float e_max, float tau_rel, void* stream);
+                      int n_codes, float e_max, float tau_rel, int* status, void* stream);
 
 /* FP16 copy of [rows, 256] FP32 values (the residual before the first layer). */
 int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream);

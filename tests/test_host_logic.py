@@ -33,7 +33,7 @@ def test_library_exports_every_declared_symbol():
         assert n_args == len(_native.SIGNATURES[name]), name
     assert set(_native.SIGNATURES) == {n for n, _ in declared}
     lib.fm_abi_version.restype = ctypes.c_int
-    assert lib.fm_abi_version() == 1
+    assert lib.fm_abi_version() == 2
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
