@@ -26,6 +26,8 @@ SIGNATURES: dict[str, list] = {
     "fm_rvq_decode_f32": [_P, _P, _P, _LL, _I, _I, _P, _P],
     "fm_band_attn_prefill_bf16": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_prefill_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
+    "fm_attention_fused_bf16": [_P, _P, _P, _P, _LL, _P, _I, _I, _I, _F, _I, _P, _P],
+    "fm_attention_chunk_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_prefill_static_bf16": [_P, _P, _P, _P, _LL, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_decode_step_bf16": [_P, _P, _P, _P, _LL, _P, _I, _P, _P, _P, _P, _I, _I, _F, _I, _P, _P],
     "fm_ring_attn_decode_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
@@ -69,5 +71,6 @@ def check(rc: int, what: str) -> None:
     if rc != 0:
         kind = {-1: "rejected geometry", -2: "grid too large", -3: "misaligned pointer",
                 -4: "cuTensorMapEncodeTiled unavailable",
-                -5: "more frames than the built-in workspace holds"}.get(rc, "CUDA error" if rc > 0 else "error")
+                -5: "more frames than the built-in workspace holds",
+                -6: "clip length outside the fused kernel's range (128 < T <= 256)"}.get(rc, "CUDA error" if rc > 0 else "error")
         raise RuntimeError(f"{what} failed with status {rc} ({kind})")

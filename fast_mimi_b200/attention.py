@@ -12,8 +12,13 @@ and load the same state dict.  Two execution modes, no fallback between them:
                      including chunked calls with a cache.
 
 ``o_proj`` (inside the reference call's return value, src/fast_mimi/model.py:1961) runs on the same
-tensor-core GEMM kernel for calls without cache (``ops.out_proj``); for one-frame streaming steps and in
-FP32 mode it is a PyTorch linear on the kernel's FP32 output.
+tensor-core GEMM kernel (``ops.out_proj``); in FP32 mode it is a PyTorch linear on the kernel's FP32 output.
+
+Cached calls (``past_key_values`` = a ``MimiKVRing``): one new frame per stream takes the ring-decode kernels,
+several new frames (chunked streaming, src/fast_mimi/model.py:2176-2205) take ``ops.attention_chunk``.
+
+The kernels never synchronise and report a timed-out device wait only through the device status word: call
+``fast_mimi_b200.check_status()`` wherever the surrounding code synchronises anyway (before results leave the GPU).
 """
 from __future__ import annotations
 
@@ -177,8 +182,11 @@ class MimiAttentionB200(nn.Module):
             core = self._forward_fp32(hidden_states, past_key_values, cos, sin)
         else:
             core = self._forward_tc(hidden_states, past_key_values, cos, sin)
-            if past_key_values is None and self.o_proj.bias is None:
-                # the kernel's 16-bit result feeds the output projection as it is
+            if self.o_proj.bias is None:
+                # the kernels' 16-bit result feeds the output projection as it is (the one-frame decode kernel
+                # returns FP32, rounded here once)
+                if core.dtype not in ops._VALUE_CODES:
+                    core = core.to(self.value_dtype)
                 out_dtype = hidden_states.dtype if hidden_states.dtype in ops._VALUE_CODES else torch.float16
                 out = ops.out_proj(core, self.out_weight(core.dtype), out_dtype=out_dtype)
                 return out.to(hidden_states.dtype), None
@@ -196,15 +204,18 @@ class MimiAttentionB200(nn.Module):
                                          value_dtype=self.value_dtype)
         if not isinstance(cache, MimiKVRing):
             raise RuntimeError("the tensor-core path needs a MimiKVRing cache (see new_cache)")
-        if T != 1:
-            raise RuntimeError("the tensor-core path streams one frame per cached call; use precision='fp32' "
-                               "for multi-frame cached chunks")
         ops._need(cache.num_streams == B, "cache was created for a different number of streams")
+        ops._need(cache.sliding_window == self.sliding_window, "cache window differs from the module's")
         pos = cache.get_seq_length(self.layer_idx)
-        out = ops.decode_step(x.view(B, 512), w, cos, sin, cache.ring_k[self.layer_idx], cache.ring_v[self.layer_idx],
-                              pos, scale=self.scaling)
-        cache.advance(self.layer_idx, 1)
-        return out.view(B, 1, 512)
+        ring_k, ring_v = cache.ring_k[self.layer_idx], cache.ring_v[self.layer_idx]
+        if T == 1:
+            out = ops.decode_step(x.view(B, 512), w, cos, sin, ring_k, ring_v, pos, scale=self.scaling)
+        else:
+            # several new frames on top of the cache: chunked streaming (src/fast_mimi/model.py:2176-2205)
+            out = ops.attention_chunk(x, w, cos, sin, ring_k, ring_v, pos, window=self.sliding_window,
+                                      scale=self.scaling)
+        cache.advance(self.layer_idx, T)
+        return out.view(B, T, 512)
 
     def _forward_fp32(self, hidden_states, cache, cos, sin):
         B, T, _ = hidden_states.shape

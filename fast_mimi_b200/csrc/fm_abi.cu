@@ -98,6 +98,39 @@ int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos
   return fm_band_attn_prefill_bf16(q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype & 1, status, stream);
 }
 
+int fm_attention_fused_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                            void* out, int B, int T, int window, float scale, int value_dtype, int* status,
+                            void* stream) {
+  if (B < 0 || T < 0 || value_dtype < 0 || value_dtype > 3) return -1;
+  if (B == 0 || T == 0) return 0;
+  if (T <= 128 || T > 256) return -6;      // only whole clips of two 128-frame tiles
+  return fm::launch_attn_fused_clip(x, w_qkv, cos, sin, cos_bstride, out, B, T, window, scale, value_dtype, status,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int fm_attention_chunk_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                            void* q_ws, void* k_ws, void* v_ws, void* k_lin, void* v_lin, void* ring_k, void* ring_v,
+                            void* out, int S, int T, int past, int ring_slots, int window, float scale, int value_dtype,
+                            int* status, void* stream) {
+  if (S < 0 || T < 0 || past < 0 || window <= 0 || ring_slots < window || value_dtype < 0 || value_dtype > 3) return -1;
+  if (ring_k == nullptr || ring_v == nullptr) return -1;
+  if (S == 0 || T == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = fm_qkv_rope_bf16(x, w_qkv, cos, sin, cos_bstride, q_ws, k_ws, v_ws, S, T, value_dtype, status, stream);
+  if (rc != 0) return rc;
+  const int delta = past < window - 1 ? past : window - 1;     // cached rows this call can still see
+  if (delta == 0) {
+    rc = fm::launch_band_attn_prefill(q_ws, k_ws, v_ws, out, S, T, window, scale, value_dtype & 1, status, st);
+  } else {
+    if (k_lin == nullptr || v_lin == nullptr) return -1;
+    rc = fm::launch_ring_linearize(ring_k, ring_v, k_ws, v_ws, k_lin, v_lin, S, T, delta, past, ring_slots, st);
+    if (rc != 0) return rc;
+    rc = fm::launch_band_attn_chunk(q_ws, k_lin, v_lin, out, S, T, delta + T, window, scale, value_dtype & 1, status, st);
+  }
+  if (rc != 0) return rc;
+  return fm::launch_ring_append(k_ws, v_ws, ring_k, ring_v, S, T, past, ring_slots, st);
+}
+
 int fm_out_proj_f16(const void* attn, const void* w_o, const float* layer_scale, const void* residual, void* y,
                     long long frames, int value_dtype, int* status, void* stream) {
   if (frames < 0 || frames > 0x7fffffffLL || value_dtype < 0 || value_dtype > 3) return -1;

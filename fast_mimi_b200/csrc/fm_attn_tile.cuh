@@ -133,5 +133,50 @@ __device__ __forceinline__ void stage_output_row2(uint32_t oa_addr, uint32_t ob_
     }
   }
 }
+// This thread's 64 output values from TMEM, normalised, rounded, straight to its frame's 128 bytes in global
+// memory (`dst` null: the loads still run, they are warp-collective, but nothing is stored).
+template <typename VT>
+__device__ __forceinline__ void store_output_row(uint32_t o_addr, uint16_t* dst, float inv) {
+#pragma unroll
+  for (int d0 = 0; d0 < kD; d0 += 32) {
+    uint32_t o[32];
+    tmem_ld32(o_addr + d0, o);
+    tmem_ld_wait();
+    if (dst != nullptr) {
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          w[e] = Pack16<VT>::pack(__uint_as_float(o[8 * cc + 2 * e]) * inv, __uint_as_float(o[8 * cc + 2 * e + 1]) * inv);
+        reinterpret_cast<uint4*>(dst + d0)[cc] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+}
+// Same for the weighted sum of two partial outputs:  c_a * O_a + c_b * O_b.
+template <typename VT>
+__device__ __forceinline__ void store_output_row2(uint32_t oa_addr, uint32_t ob_addr, uint16_t* dst, float c_a, float c_b) {
+#pragma unroll
+  for (int d0 = 0; d0 < kD; d0 += 32) {
+    uint32_t oa[32], ob[32];
+    tmem_ld32(oa_addr + d0, oa);
+    tmem_ld32(ob_addr + d0, ob);
+    tmem_ld_wait();
+    if (dst != nullptr) {
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 8 * cc + 2 * e;
+          w[e] = Pack16<VT>::pack(fmaf(__uint_as_float(oa[j]), c_a, __uint_as_float(ob[j]) * c_b),
+                                  fmaf(__uint_as_float(oa[j + 1]), c_a, __uint_as_float(ob[j + 1]) * c_b));
+        }
+        reinterpret_cast<uint4*>(dst + d0)[cc] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+}
 }  // namespace attn_tile
 }  // namespace fm

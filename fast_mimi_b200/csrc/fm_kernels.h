@@ -67,6 +67,19 @@ int launch_rvq_decode(const long long* codes, const float* codebooks, float* out
                       int n_codes, int* bad_code, cudaStream_t st);
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st);
+// Queries [B, Tq, 512] against keys / values [B, Tk, 512], Tk >= Tq: the last Tq key rows are the queries' own
+// frames, the Tk - Tq rows before them are older (cached) frames.
+int launch_band_attn_chunk(const void* q, const void* k, const void* v, void* out, int B, int Tq, int Tk, int window,
+                           float scale, int value_is_fp16, int* status, cudaStream_t st);
+// KV ring <-> frame-major tensors for multi-frame cached calls (fm_ring.cu).
+int launch_ring_linearize(const void* ring_k, const void* ring_v, const void* k_new, const void* v_new, void* k_lin,
+                          void* v_lin, int S, int T, int delta, int past, int slots, cudaStream_t st);
+int launch_ring_append(const void* k_new, const void* v_new, void* ring_k, void* ring_v, int S, int T, int past,
+                       int slots, cudaStream_t st);
+// Projection + RoPE + banded attention in one kernel for 128 < T <= 256 (fm_fused_clip.cu): q, k, v stay on chip.
+int launch_attn_fused_clip(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                           void* out, int B, int T, int window, float scale, int dtype_flags, int* status,
+                           cudaStream_t st);
 int launch_band_attn_clip(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                           float scale, int value_is_fp16, int* status, cudaStream_t st);
 int launch_band_attn_long(const void* q, const void* k, const void* v, void* out, int B, int T, int window,

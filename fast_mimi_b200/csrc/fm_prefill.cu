@@ -13,6 +13,11 @@
 // with TMEM accumulators; the softmax warps own one query row per thread (tcgen05.ld 32x32b), keep
 // the running maximum / sum / output in registers, and hand P_j back through shared memory as a
 // K-major swizzled 16-bit tile.  Warps 0-3: softmax + output.  Warp 4: TMA + MMA issue.
+//
+// The same kernel serves calls whose keys start before their queries (a chunk of new frames attending to
+// cached frames plus itself, src/fast_mimi/model.py:2194-2205 with query_offset = past and key_offset =
+// max(past - (W-1), 0)): query row i of Tq sits `delta` = query_offset - key_offset rows further along the
+// key axis, key row j of Tk = delta + Tq is visible iff  i + delta - W < j <= i + delta.
 #include "fm_common.cuh"
 #include "fm_kernels.h"
 
@@ -46,8 +51,8 @@ static_assert(sizeof(Barriers) <= 256, "barrier block too large");
 template <typename VT>
 __global__ void __launch_bounds__(fmha::kThreads, 2)
 band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                         const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ out, int T,
-                         int window, float scale_log2e, int* status) {
+                         const __grid_constant__ CUtensorMap tmap_v, uint16_t* __restrict__ out, int T, int Tk,
+                         int delta, int window, float scale_log2e, int* status) {
   using namespace fmha;
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
 
@@ -62,9 +67,10 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   const int lane = threadIdx.x & 31;
   const int qt = blockIdx.x, head = blockIdx.y, clip = blockIdx.z;
   const int q0 = qt * kTile;
-  int j_lo = (q0 - (window - 1)) / kTile;   // first key tile touching the band (q0 >= 0 so C division is fine
-  if (q0 - (window - 1) < 0) j_lo = 0;      //  once negative starts are clamped)
-  const int j_hi = qt;
+  const int band_lo = q0 + delta - (window - 1);            // oldest key row any query of the tile may see
+  const int j_lo = band_lo > 0 ? band_lo / kTile : 0;       // first key tile touching the band
+  const int band_hi = q0 + kTile - 1 + delta < Tk - 1 ? q0 + kTile - 1 + delta : Tk - 1;
+  const int j_hi = band_hi / kTile;                         // == qt when keys and queries coincide
   const int n_kv = j_hi - j_lo + 1;
 
   if (threadIdx.x == 0) {
@@ -161,15 +167,15 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     for (int jj = 0; jj < n_kv; ++jj) {
       const int k0 = (j_lo + jj) * kTile;
       // A tile needs per-element masking if it crosses the causal diagonal or the window's lower edge.
-      const bool need_mask = (k0 + kTile - 1 > q0) || (k0 < q0 + kTile - window);
-      const int vis_lo = i - window + 1 - k0;   // visible columns c: vis_lo <= c <= vis_hi
-      const int vis_hi = i - k0;
+      const bool need_mask = (k0 + kTile - 1 > q0 + delta) || (k0 < q0 + delta + kTile - window);
+      const int vis_lo = i + delta - window + 1 - k0;   // visible columns c: vis_lo <= c <= vis_hi
+      const int vis_hi = i + delta - k0;
       mbar_wait(&bars->s_full, static_cast<uint32_t>(jj) & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
 
       // A 32-column group is skipped by the whole warp when none of the warp's 32 rows can see it.
-      const int warp_vis_lo = q0 + warp * 32 - window + 1 - k0;   // smallest visible column of any row
-      const int warp_vis_hi = q0 + warp * 32 + 31 - k0;           // largest
+      const int warp_vis_lo = q0 + delta + warp * 32 - window + 1 - k0;   // smallest visible column of any row
+      const int warp_vis_hi = q0 + delta + warp * 32 + 31 - k0;           // largest
       // Pass 1: row maximum of the visible scores (log2 domain).
       float m_tile = -INFINITY;
 #pragma unroll 1
@@ -279,6 +285,38 @@ static int encode_clip_tile(CUtensorMap* map, const void* base, int B, int T, CU
   return encode_tiled(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+static int launch_general(const void* q, const void* k, const void* v, void* out, int B, int T, int Tk, int delta,
+                          int window, float scale, int value_is_fp16, int* status, cudaStream_t st) {
+  using namespace fmha;
+  if (B > 65535) return -1;
+  CUtensorMap tq, tk, tv;
+  int rc = encode_clip_tile(&tq, q, B, T, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  if (rc != 0) return rc;
+  rc = encode_clip_tile(&tk, k, B, Tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  if (rc != 0) return rc;
+  rc = encode_clip_tile(&tv, v, B, Tk, value_is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  if (rc != 0) return rc;
+  auto kern = value_is_fp16 ? band_attn_prefill_kernel<__half> : band_attn_prefill_kernel<__nv_bfloat16>;
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
+  if (rc != 0) return rc;
+  dim3 grid((T + kTile - 1) / kTile, 8, B);
+  const float scale_log2e = scale * 1.4426950408889634f;
+  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, static_cast<uint16_t*>(out), T, Tk, delta, window, scale_log2e,
+                                          status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_band_attn_chunk(const void* q, const void* k, const void* v, void* out, int B, int Tq, int Tk, int window,
+                           float scale, int value_is_fp16, int* status, cudaStream_t st) {
+  if (B <= 0 || Tq <= 0) return (B == 0 || Tq == 0) ? 0 : -1;
+  if (window <= 0 || Tk < Tq) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(out)) & 15u)
+    return -3;
+  if (Tk == Tq) return launch_band_attn_prefill(q, k, v, out, B, Tq, window, scale, value_is_fp16, status, st);
+  return launch_general(q, k, v, out, B, Tq, Tk, Tk - Tq, window, scale, value_is_fp16, status, st);
+}
+
 int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* out, int B, int T, int window,
                              float scale, int value_is_fp16, int* status, cudaStream_t st) {
   using namespace fmha;
@@ -293,20 +331,7 @@ int launch_band_attn_prefill(const void* q, const void* k, const void* v, void* 
   // Longer clips whose window spans exactly three key tiles per query tile take the run-walking kernel.
   if (T > 2 * kTile && window > kTile + 1 && window <= 2 * kTile + 1 && B <= (1 << 27))
     return launch_band_attn_long(q, k, v, out, B, T, window, scale, value_is_fp16, status, st);
-  CUtensorMap tq, tk, tv;
-  int rc = encode_clip_tile(&tq, q, B, T, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-  if (rc != 0) return rc;
-  rc = encode_clip_tile(&tk, k, B, T, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-  if (rc != 0) return rc;
-  rc = encode_clip_tile(&tv, v, B, T, value_is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-  if (rc != 0) return rc;
-  auto kern = value_is_fp16 ? band_attn_prefill_kernel<__half> : band_attn_prefill_kernel<__nv_bfloat16>;
-  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
-  if (rc != 0) return rc;
-  dim3 grid((T + kTile - 1) / kTile, 8, B);
-  const float scale_log2e = scale * 1.4426950408889634f;
-  kern<<<grid, kThreads, kSmemBytes, st>>>(tq, tk, tv, static_cast<uint16_t*>(out), T, window, scale_log2e, status);
-  return static_cast<int>(cudaGetLastError());
+  return launch_general(q, k, v, out, B, T, T, 0, window, scale, value_is_fp16, status, st);
 }
 
 }  // namespace fm

@@ -52,6 +52,32 @@ class MimiKVRing:
     def advance(self, layer_idx: int, frames: int) -> None:
         self._cumulative_lengths[layer_idx] += frames
 
+    def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """``MimiKVCache.update`` (src/fast_mimi/model.py:435-471) on ring storage, for a caller that projects and
+        rotates K / V itself (the reference's own attention module): ``key_states, value_states [streams, 8, T, 64]``
+        are the call's new rows; returns the visible rows for this call (the newest ``window - 1`` cached rows in
+        position order, then the new rows), in the callers' dtype, and stores the new rows in their slots.  The
+        B200 attention module does not go through here: its kernels write the ring themselves."""
+        past = self.get_seq_length(layer_idx)
+        w = self.sliding_window
+        T = key_states.shape[2]
+        keep = min(past, w - 1)
+        old = (torch.arange(past - keep, past, device=self.ring_k.device) % w)
+        k_old = self.ring_k[layer_idx][:, :, old].to(key_states.dtype)
+        v_old = self.ring_v[layer_idx][:, :, old].to(value_states.dtype)
+        first = max(T - w, 0)
+        slots = (torch.arange(past + first, past + T, device=self.ring_k.device) % w)
+        self.ring_k[layer_idx][:, :, slots] = key_states[:, :, first:].to(self.ring_k.dtype)
+        self.ring_v[layer_idx][:, :, slots] = value_states[:, :, first:].to(self.ring_v.dtype)
+        self.advance(layer_idx, T)
+        return torch.cat((k_old, key_states), dim=2), torch.cat((v_old, value_states), dim=2)
+
+    def to(self, device) -> "MimiKVRing":
+        """Move the rings to ``device`` (``MimiKVCache.to``, src/fast_mimi/model.py:507)."""
+        self.ring_k = self.ring_k.to(device)
+        self.ring_v = self.ring_v.to(device)
+        return self
+
     def reset(self) -> None:
         self._cumulative_lengths = [0] * self.num_layers
 

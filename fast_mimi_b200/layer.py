@@ -5,15 +5,15 @@
 (``self_attn``, ``mlp.fc1``, ``mlp.fc2``, ``input_layernorm``, ``post_attention_layernorm``,
 ``self_attn_layer_scale.scale``, ``mlp_layer_scale.scale``), so state dicts are interchangeable.
 
-For calls without cache the whole layer runs on this package's kernels, seven launches:
+The whole layer runs on this package's kernels, seven launches for a call without cache:
 
     LayerNorm -> QKV projection + RoPE -> banded attention -> o_proj + layer scale + residual
               -> LayerNorm -> fc1 + GELU -> fc2 + layer scale + residual
 
 The residual stream keeps the caller's dtype (FP32 stays FP32: both residual adds happen in the FP32 epilogue
-of a GEMM); only the operands of the tensor-core products are rounded to 16 bit.  Streaming calls with a
-cache (one frame per stream) use the attention module's ring-decode path and PyTorch for the small
-LayerNorm / MLP products around it.
+of a GEMM); only the operands of the tensor-core products are rounded to 16 bit.  Calls with a cache (a
+``MimiKVRing``) differ only in the attention core: ring decode for one new frame per stream, the chunk path for
+several; LayerNorms, projections and the MLP are the same kernels.
 """
 from __future__ import annotations
 
@@ -94,13 +94,6 @@ class MimiTransformerLayerB200(nn.Module):
     def forward(self, hidden_states: torch.Tensor, attention_mask: torch.Tensor | None, past_key_values,
                 position_embeddings: tuple[torch.Tensor, torch.Tensor], output_attentions: bool = False,
                 canonical_window_mask: bool = False) -> tuple[torch.Tensor, torch.Tensor | None]:
-        if past_key_values is not None:
-            # streaming step: a handful of frames; the ring-decode kernels carry the attention
-            attention_output, weights = self.self_attn(self.input_layernorm(hidden_states), attention_mask,
-                                                       past_key_values, position_embeddings, output_attentions,
-                                                       canonical_window_mask)
-            hidden_states = hidden_states + self.self_attn_layer_scale(attention_output)
-            return hidden_states + self.mlp_layer_scale(self.mlp(self.post_attention_layernorm(hidden_states))), weights
         if output_attentions:
             raise RuntimeError("attention probabilities are not materialised by the B200 kernels")
         if not hidden_states.is_cuda:
@@ -117,8 +110,13 @@ class MimiTransformerLayerB200(nn.Module):
         ln1, ln2 = self.input_layernorm, self.post_attention_layernorm
         f32 = lambda p: p.detach().float().contiguous()       # no copy for FP32 parameters
         h = ops.layer_norm(x, f32(ln1.weight), f32(ln1.bias), eps=ln1.eps, out_dtype=tc)
-        core = ops.attention_prefill(h, attn.packed_qkv_weight(tc), cos, sin, window=attn.sliding_window,
-                                     scale=attn.scaling, value_dtype=attn.value_dtype)
+        if past_key_values is None:
+            core = ops.attention_prefill(h, attn.packed_qkv_weight(tc), cos, sin, window=attn.sliding_window,
+                                         scale=attn.scaling, value_dtype=attn.value_dtype)
+        else:
+            core = attn._forward_tc(h, past_key_values, cos, sin)      # ring decode (FP32 result) or chunk path
+            if core.dtype not in ops._VALUE_CODES:
+                core = core.to(attn.value_dtype)
         x1 = ops.linear(core, attn.out_weight(core.dtype), scale=f32(self.self_attn_layer_scale.scale), residual=x,
                         out_dtype=stream_dtype)
         h2 = ops.layer_norm(x1, f32(ln2.weight), f32(ln2.bias), eps=ln2.eps, out_dtype=tc)

@@ -258,6 +258,72 @@ def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtyp
     return out
 
 
+def attention_fused(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtype=torch.float16, out=None, status=None):
+    """Projection + RoPE + banded attention in one kernel for clips of 128 < T <= 256 frames: ``x [B,T,512]`` ->
+    ``[B,T,512]`` value_dtype, no q / k / v workspace (they stay in shared and tensor memory)."""
+    lib = _native.load()
+    _need(x.dim() == 3, "x must be [B, T, 512]")
+    B, T, _ = x.shape
+    _need(128 < T <= 256, "the fused kernel takes clips of 129 .. 256 frames")
+    in_flag = _check_projection_inputs(x, w_qkv)
+    bstride = _check_tables(cos, sin, B, T)
+    _need(value_dtype in _VALUE_CODES, "value_dtype must be float16 or bfloat16")
+    if out is None:
+        out = torch.empty(x.shape, dtype=value_dtype, device=x.device)
+    _check_frames(out, "out", value_dtype, B * T)
+    rc = lib.fm_attention_fused_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
+                                     out.data_ptr(), B, T, window, scale, _VALUE_CODES[value_dtype] | in_flag,
+                                     _status_ptr(status, x), _stream())
+    _native.check(rc, "fm_attention_fused_bf16")
+    return out
+
+
+def attention_chunk(x, w_qkv, cos, sin, ring_k, ring_v, past, *, window=250, scale=0.125, workspace=None, out=None,
+                    status=None):
+    """A cached call with ``T`` new frames per stream: ``x [S,T,512]`` at absolute positions ``past .. past+T-1``
+    (``cos, sin [1 or S, T, 64]`` are their tables) attends to the ``min(past, window-1)`` newest frames already in
+    the ring plus itself, then the new rotated K / V rows enter the ring ``[S,8,slots,64]``.  Returns
+    ``[S,T,512]`` in the ring's value type.  ``workspace``: optional ``(q, k, v, k_lin, v_lin)`` buffers of
+    ``[S,T,512]`` (bf16, bf16, value type) and ``[S, min(past, window-1) + T, 512]`` (bf16, value type)."""
+    lib = _native.load()
+    _need(x.dim() == 3, "x must be [S, T, 512]")
+    S, T, _ = x.shape
+    past = int(past)
+    _need(past >= 0, "past must not be negative")
+    in_flag = _check_projection_inputs(x, w_qkv)
+    bstride = _check_tables(cos, sin, S, T)
+    _need(ring_k.dim() == 4 and ring_k.shape[0] == S and ring_k.shape[1] == HEADS and ring_k.shape[3] == HEAD_DIM
+          and ring_k.is_cuda and ring_k.dtype == torch.bfloat16 and ring_k.is_contiguous(),
+          "ring_k must be contiguous bf16 [S, 8, slots, 64]")
+    _need(ring_v.is_cuda and ring_v.dtype in _VALUE_CODES and ring_v.is_contiguous() and ring_v.shape == ring_k.shape,
+          "ring_v must match ring_k (float16 or bfloat16)")
+    slots = ring_k.shape[2]
+    _need(slots >= window, "the ring must have at least `window` slots")
+    vdt = ring_v.dtype
+    delta = min(past, window - 1)
+    if workspace is None:
+        mk = lambda rows, dt: torch.empty((S, rows, HIDDEN), dtype=dt, device=x.device)
+        workspace = (mk(T, torch.bfloat16), mk(T, torch.bfloat16), mk(T, vdt),
+                     mk(delta + T, torch.bfloat16) if delta else None, mk(delta + T, vdt) if delta else None)
+    q, k, v, k_lin, v_lin = workspace
+    _check_frames(q, "q workspace", torch.bfloat16, S * T)
+    _check_frames(k, "k workspace", torch.bfloat16, S * T)
+    _check_frames(v, "v workspace", vdt, S * T)
+    if delta:
+        _check_frames(k_lin, "k_lin workspace", torch.bfloat16, S * (delta + T))
+        _check_frames(v_lin, "v_lin workspace", vdt, S * (delta + T))
+    if out is None:
+        out = torch.empty(x.shape, dtype=vdt, device=x.device)
+    _check_frames(out, "out", vdt, S * T)
+    rc = lib.fm_attention_chunk_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
+                                     q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_lin) if delta else None,
+                                     _ptr(v_lin) if delta else None, ring_k.data_ptr(), ring_v.data_ptr(), out.data_ptr(),
+                                     S, T, past, slots, window, scale, _VALUE_CODES[vdt] | in_flag,
+                                     _status_ptr(status, x), _stream())
+    _native.check(rc, "fm_attention_chunk_bf16")
+    return out
+
+
 STATIC_MAX_FRAMES = 8192
 
 

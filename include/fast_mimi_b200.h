@@ -47,6 +47,29 @@ int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const f
 int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int B, int T,
                               int window, float scale, int value_dtype, int* status, void* stream);
 
+/* The same computation as fm_attention_prefill_bf16 in ONE kernel for clips of 128 < T <= 256 frames (Mimi's
+ * 10 s clips): x and W_qkv in, attention output out, the rotated q, k, v never reach memory, so no workspace.
+ * Replaces src/fast_mimi/model.py:1897-1914 + :1627-1688 + :1860-1868 for such clips (the reference's own fused
+ * front half: src/fast_mimi/_packed_qkv.py:14-131,152-202).  Other T: returns -6 (use fm_attention_prefill_bf16,
+ * which routes here by itself when T fits).  value_dtype as for fm_qkv_rope_bf16. */
+int fm_attention_fused_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                            void* out, int B, int T, int window, float scale, int value_dtype, int* status,
+                            void* stream);
+
+/* A call with T >= 1 new frames per stream on top of a KV ring that already holds `past` frames: the cached
+ * multi-frame call of the reference (chunked streaming encode: MimiAttention.forward with q_len > 1 and a cache,
+ * src/fast_mimi/model.py:1912-1914; keys = the last window-1 cached rows + the new rows, MimiKVCache.update
+ * src/fast_mimi/model.py:450-471; band with query_offset = past, key_offset = max(past - (window-1), 0),
+ * src/fast_mimi/model.py:2194-2205, :1672-1677).  Projection + RoPE into q_ws / k_ws / v_ws [S, T, 512]; when
+ * past > 0 the still-visible ring rows and the new rows are laid out frame-major in k_lin / v_lin
+ * [S, min(past, window-1) + T, 512] (may be NULL when past == 0); banded attention writes out [S, T, 512]
+ * (value type); finally the newest min(T, ring_slots) new rows enter the ring [S, 8, ring_slots, 64] at slot
+ * position % ring_slots.  cos / sin are the tables of positions past .. past+T-1.  ring_slots >= window. */
+int fm_attention_chunk_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
+                            void* q_ws, void* k_ws, void* v_ws, void* k_lin, void* v_lin, void* ring_k, void* ring_v,
+                            void* out, int S, int T, int past, int ring_slots, int window, float scale, int value_dtype,
+                            int* status, void* stream);
+
 /* y = residual + layer_scale * (attn W_o^T): the output projection that follows the attention core
  * (src/fast_mimi/model.py:1961) with the layer scale and residual add of the transformer layer
  * (src/fast_mimi/model.py:2059) folded into the FP32 epilogue.  Same persistent tensor-core kernel as

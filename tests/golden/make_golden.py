@@ -158,6 +158,38 @@ def cached_streams(name, cfg, b, chunks, seed, keep_steps=None, std=0.2, bf16_in
     save(name, **arrays)
 
 
+def cached_chunks_mimi(name="cached_chunks_mimi.npz", chunks=(12, 50, 1, 200, 1, 37, 260, 3), b=2, seed=21):
+    """The reference's chunked streaming scenario (tests/test_parity.py:56-81 of the reference) at Mimi's own
+    geometry: one MimiAttention layer + MimiKVCache driven with the caller bookkeeping of model.py:2176-2206,
+    BF16-representable weights and inputs.  The chunk lengths cross the window (12+50+1+200 = 263 > 250), include
+    one-frame steps between chunks and a chunk longer than the window.  Inputs are regenerated from the seed;
+    every fifth output row of each chunk (plus its first and last) is stored."""
+    cfg = MimiConfig()
+    torch.manual_seed(seed)
+    attn = MimiAttention(cfg, 0, "sdpa").eval()
+    for p in attn.parameters():
+        torch.nn.init.normal_(p, std=0.02)
+    _round_bf16_(attn)
+    rope = MimiRotaryEmbedding(cfg)
+    cache = MimiKVCache(1, sliding_window=cfg.sliding_window)
+    arrays = dict(seed=seed, b=b, chunks=np.array(chunks))
+    for step, t in enumerate(chunks):
+        x = torch.randn(b, t, cfg.hidden_size).bfloat16().float()
+        past = cache.get_seq_length()
+        k_len, k_off = cache.get_mask_sizes(t)
+        mask = _attention_mask(batch_size=b, query_length=t, key_length=k_len, query_offset=past, key_offset=k_off,
+                               sliding_window=cfg.sliding_window, padding_mask=None, backend="sdpa", dtype=x.dtype,
+                               device=x.device)
+        with torch.inference_mode():
+            out, _ = attn(x, mask, cache, rope(x, torch.arange(past, past + t)[None]))
+        rows = np.array(sorted(set(list(range(0, t, 5)) + [t - 1])))
+        arrays[f"rows{step}"] = rows
+        arrays[f"out{step}"] = out[:, rows]
+    arrays.update(final_key_cache=cache.key_cache[0][:, :, -3:], final_value_cache=cache.value_cache[0][:, :, -3:],
+                  seq_length=cache.get_seq_length())
+    save(name, **arrays)
+
+
 def transformer_stack_tiny():
     """Two-layer tiny MimiTransformerModel, prefill then cached steps (shared cache, layer
     positions taken from layer 0 as the reference does)."""
@@ -261,6 +293,7 @@ if __name__ == "__main__":
     cached_streams("tiny_cached_decode.npz", tiny_config(), 1, [1] * 12, seed=13)
     cached_streams("ring_decode_260.npz", MimiConfig(), 2, [1] * 260, seed=5, std=0.02,
                    keep_steps={0, 1, 2, 127, 248, 249, 250, 251, 259}, bf16_inputs=True)
+    cached_chunks_mimi()
     transformer_stack_tiny()
     for seconds in (5, 10, 12):
         end_to_end_codes(seconds)

@@ -252,6 +252,134 @@ def test_streaming_decode_260_steps_matches_reference():
     assert O.rel_l2(v_ord[:, :, -3:].float().cpu(), g["final_value_cache"]) < 5e-4
 
 
+def _module_with_weights(ws):
+    """``ws``: four [512, 512] weights (q, k, v, o) or a fixture seed.  The module is built BEFORE a seed's
+    weights are regenerated: its own default initialisation consumes the global RNG, and the fixtures' inputs
+    are drawn right after their weights."""
+    import fast_mimi_b200 as fm
+    m = fm.MimiAttentionB200().cuda()
+    if isinstance(ws, int):
+        ws = regen_projections(ws)
+    with torch.no_grad():
+        for dst, src in zip((m.q_proj, m.k_proj, m.v_proj, m.o_proj), ws):
+            dst.weight.copy_(src)
+    return m
+
+
+def test_cached_multi_frame_chunks_match_reference():
+    """Chunked streaming through the tensor-core path: every call carries several new frames on top of the KV
+    ring (the reference's scenario of tests/test_parity.py:56-81 at Mimi's geometry: chunks that cross the
+    window, one-frame steps between them, a chunk longer than the window) vs the reference's MimiAttention +
+    MimiKVCache outputs; the ring must end up holding the reference cache's rows."""
+    g = load_golden("cached_chunks_mimi.npz")
+    m = _module_with_weights(int(g["seed"]))
+    b = int(g["b"])
+    cache = m.new_cache(1, b, "cuda")
+    for step, t in enumerate(g["chunks"].tolist()):
+        x = torch.randn(b, t, 512).bfloat16().float()
+        past = cache.get_seq_length()
+        cos, sin = O.rope_tables(torch.arange(past, past + t))
+        out, _ = m(x.cuda(), None, cache, (cos.cuda()[None], sin.cuda()[None]))
+        err = O.rel_l2(out.cpu()[:, g[f"rows{step}"]], g[f"out{step}"])
+        print(f"chunk {step} (T={t}, past={past}): rel-L2 {err:.2e}")
+        assert err < TOL, (step, t, err)
+    assert cache.get_seq_length() == int(g["seq_length"])
+    k_ord, v_ord = cache.ordered(0)
+    assert O.rel_l2(k_ord[:, :, -3:].float().cpu(), g["final_key_cache"]) < TOL_BF16_STORE
+    assert O.rel_l2(v_ord[:, :, -3:].float().cpu(), g["final_value_cache"]) < 5e-4
+    import fast_mimi_b200 as fm
+    fm.check_status()
+
+
+@pytest.mark.parametrize("chunks", [[300, 1, 1], [250, 7, 1], [1, 1, 128, 129, 1], [5, 256, 257, 2]])
+def test_prefill_into_ring_then_stream_equals_full_prefill(chunks):
+    """Seeding the ring with a multi-frame call and continuing with chunks / single frames gives the rows of one
+    cache-free prefill over the concatenated frames (the band mask makes both see the same keys)."""
+    torch.manual_seed(17)
+    m = _module_with_weights([torch.randn(512, 512) * 0.03 for _ in range(4)])
+    total = sum(chunks)
+    x = torch.randn(2, total, 512).bfloat16().float().cuda()
+    cos, sin = (t.cuda()[None] for t in O.rope_tables(torch.arange(total)))
+    full, _ = m(x, None, None, (cos, sin))
+    cache = m.new_cache(1, 2, "cuda")
+    a = 0
+    for t in chunks:
+        out, _ = m(x[:, a:a + t], None, cache, (cos[:, a:a + t], sin[:, a:a + t]))
+        err = O.rel_l2(out.float().cpu(), full[:, a:a + t].float().cpu())
+        assert err < TOL, (chunks, a, t, err)
+        a += t
+
+
+def test_ring_update_matches_reference_cache_semantics():
+    """MimiKVRing.update (the MimiKVCache.update-compatible entry for callers that rotate K / V themselves):
+    visible rows and survivors follow src/fast_mimi/model.py:450-471."""
+    import fast_mimi_b200 as fm
+    ring = fm.MimiKVRing(1, 2, 8, device="cuda")
+    ref = O.KVCacheOracle(window=8)
+    g = torch.Generator().manual_seed(3)
+    for t in (3, 1, 9, 2, 1):       # values that the ring's BF16 / FP16 storage holds exactly
+        k = torch.randn(2, 8, t, 64, generator=g).bfloat16().float()
+        v = torch.randn(2, 8, t, 64, generator=g).half().float()
+        want_k, want_v = ref.update(k, v, 0)
+        got_k, got_v = ring.update(k.cuda(), v.cuda(), 0)
+        assert torch.equal(got_k.cpu(), want_k) and torch.equal(got_v.cpu(), want_v), t
+        assert ring.get_mask_sizes(4) == ref.get_mask_sizes(4)
+    assert ring.get_seq_length() == ref.get_seq_length() == 16
+    assert ring.to("cuda") is ring
+
+
+def test_negative_position_is_rejected_before_any_launch():
+    import fast_mimi_b200 as fm
+    ring = fm.MimiKVRing(1, 2, 250, device="cuda")
+    x = torch.zeros(2, 512, device="cuda", dtype=torch.bfloat16)
+    w = torch.zeros(1536, 512, device="cuda", dtype=torch.bfloat16)
+    cs = torch.zeros(1, 1, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        fm.ops.decode_step(x, w, cs, cs, ring.ring_k[0], ring.ring_v[0], -1)
+    lib = fm._native.load()
+    out = torch.full((2, 512), float("nan"), device="cuda")
+    st = fm.ops.new_status("cuda")
+    rc = lib.fm_decode_step_bf16(x.data_ptr(), w.data_ptr(), cs.data_ptr(), cs.data_ptr(), 0, None, -3, x.data_ptr(),
+                                 ring.ring_k[0].data_ptr(), ring.ring_v[0].data_ptr(), out.data_ptr(), 2, 250, 0.125, 1,
+                                 st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    rc = lib.fm_ring_attn_decode_bf16(x.data_ptr(), ring.ring_k[0].data_ptr(), ring.ring_v[0].data_ptr(), out.data_ptr(),
+                                      None, -1, 2, 250, 0.125, 1, st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(out).all()) and fm.ops.read_status(st) == 0
+
+
+def test_preset_status_word_makes_kernels_return_untouched_outputs():
+    """The sticky status word: a kernel handed a non-zero word must not write its outputs, and check_status must
+    raise until the word is cleared."""
+    import fast_mimi_b200 as fm
+    st = fm.ops.new_status("cuda")
+    st.fill_(101)
+    x = torch.randn(2, 250, 512, device="cuda").bfloat16()
+    w = (torch.randn(1536, 512, device="cuda") * 0.02).bfloat16()
+    cos, sin = (t.cuda()[None] for t in O.rope_tables(torch.arange(250)))
+    out = torch.full((2, 250, 512), float("nan"), device="cuda", dtype=torch.float16)
+    fm.ops.attention_prefill(x, w, cos, sin, out=out, status=st)
+    fm.ops.band_attention_prefill(x, x, x.half(), out=out, status=st)
+    x6 = torch.randn(1, 600, 512, device="cuda").bfloat16()
+    out6 = torch.full((1, 600, 512), float("nan"), device="cuda", dtype=torch.float16)
+    fm.ops.band_attention_prefill(x6, x6, x6.half(), out=out6, status=st)
+    fm.ops.band_attention_prefill(x6, x6, x6.half(), out=out6, window=64, status=st)
+    y = torch.full((2, 250, 512), float("nan"), device="cuda", dtype=torch.float16)
+    fm.ops.linear(x, w[:512].contiguous(), out=y, status=st)
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(out.float()).all()) and bool(torch.isnan(out6.float()).all()) and bool(torch.isnan(y.float()).all())
+    assert fm.ops.read_status(st) == 101
+    with pytest.raises(RuntimeError, match="101"):
+        fm.check_status(status=st)
+    st.zero_()
+    fm.check_status(status=st)
+    fm.ops.attention_prefill(x, w, cos, sin, out=out, status=st)
+    torch.cuda.synchronize()
+    assert not bool(torch.isnan(out.float()).any())
+
+
 def test_module_rejects_what_it_does_not_implement():
     import fast_mimi_b200 as fm
     m = fm.MimiAttentionB200().cuda()

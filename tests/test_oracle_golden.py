@@ -76,6 +76,21 @@ def test_tiny_cached_chunks_and_decode_match_reference():
         assert (cache.values[0] - g["final_value_cache"]).abs().max() < TOL
 
 
+def test_mimi_size_cached_chunks_match_reference():
+    """Chunked streaming at Mimi's geometry (chunks that cross the window, one-frame steps in between, one chunk
+    longer than the window): the oracle against the reference's MimiAttention + MimiKVCache outputs."""
+    g = load_golden("cached_chunks_mimi.npz")
+    wq, wk, wv, wo = regen_projections(int(g["seed"]))
+    cache = O.KVCacheOracle()
+    for step, t in enumerate(g["chunks"].tolist()):
+        x = torch.randn(int(g["b"]), t, 512).bfloat16().float()
+        out = O.attention_forward(x, wq, wk, wv, wo, cache=cache)
+        assert (out[:, g[f"rows{step}"]] - g[f"out{step}"]).abs().max() < TOL, step
+    assert cache.get_seq_length() == int(g["seq_length"])
+    assert (cache.keys[0][:, :, -3:] - g["final_key_cache"]).abs().max() < TOL
+    assert (cache.values[0][:, :, -3:] - g["final_value_cache"]).abs().max() < TOL
+
+
 def test_ring_decode_260_matches_reference():
     g = load_golden("ring_decode_260.npz")
     wq, wk, wv, wo = regen_projections(int(g["seed"]))
