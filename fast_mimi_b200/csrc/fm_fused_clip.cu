@@ -11,7 +11,8 @@
 //   projection   one pair MMA stream M = 256 frames x N = 192 (the head's q | k | v columns) x K = 512; each CTA
 //                streams HALF of the head's W slice (96 rows, 12 KB stages), so a W byte crosses L2 -> SM once per
 //                256 frames.  Accumulator: 192 TMEM columns per CTA.
-//   epilogue     4 warps (one frame row per thread): RoPE in FP32, then  Q -> tensor memory (16-bit, 32 columns),
+//   epilogue     8 warps (two threads per frame row: RoPE pair sets 0-15 / 16-31, V dimensions 0-31 / 32-63):
+//                RoPE in FP32, then  Q -> tensor memory (16-bit, 32 columns),
 //                K -> this CTA's shared memory (128 keys x 64, K-major),  V -> TRANSPOSED into BOTH CTAs' shared
 //                memory: dimensions 0-31 of every key to CTA 0, 32-63 to CTA 1 (V^T [32 d x 256 keys], K-major).
 //   scores       one pair MMA M = 256, N = 256 keys, K = 64: A = Q from each CTA's tensor memory, B = K, each CTA
@@ -25,8 +26,8 @@
 //   output       normalised in registers and written straight to global memory (128 contiguous bytes per frame-head).
 //
 // TMEM columns per CTA: [0,192) projection accumulator, [192,224) Q, [256,512) scores (P and O overlay them).
-// Warps: 0-3 epilogue, 4-7 team A, 8-11 team B, 12 W loads (+ TMEM allocation), 13 x loads, 14 projection MMAs
-// (leader CTA), 15 attention MMAs (leader CTA).  Every barrier that gates a pair MMA lives in the leader and
+// Warps: 0-7 epilogue, 8-11 team A, 12-15 team B, 16 W loads (+ TMEM allocation), 17 x loads, 18 projection MMAs
+// (leader CTA), 19 attention MMAs (leader CTA).  Every barrier that gates a pair MMA lives in the leader and
 // counts arrivals from both CTAs; completions are multicast to both.  No TMA multicast anywhere.
 #include "fm_attn_tile.cuh"
 #include "fm_common.cuh"
@@ -47,8 +48,10 @@ constexpr int kWStageBytes = kWRows * 64 * 2;     // 12 KB
 constexpr int kKParkBytes = kTile * kD * 2;       // 16 KB
 constexpr int kVtTileBytes = 32 * 64 * 2;         // 4 KB: 32 dimensions x 64 keys
 constexpr int kVtBufBytes = 4 * kVtTileBytes;     // 16 KB: 256 keys
-constexpr int kEpiWarps = 4;
-constexpr int kThreads = 16 * 32;
+constexpr int kEpiWarps = 8;
+constexpr int kTeamWarp0 = kEpiWarps;             // team A: warps 8-11, team B: warps 12-15
+constexpr int kIssueWarp0 = kEpiWarps + 8;        // W loads, x loads, projection MMAs, attention MMAs
+constexpr int kThreads = (kIssueWarp0 + 4) * 32;
 constexpr int kTmemCols = 512;
 constexpr uint32_t kAccCol = 0, kQCol = 192, kSCol = 256;
 constexpr uint32_t kOOff = 64;                    // inside a team's 128 score columns: P at +0, O at +64
@@ -59,8 +62,8 @@ struct Shared {
   uint64_t w_full[kWStages];    // leader: both halves of a W stage have landed
   uint64_t w_empty[kWStages];   // per CTA: stage consumed
   uint64_t acc_full;            // per CTA: the head's projection is complete
-  uint64_t acc_empty;           // leader: 8 epilogue warps have read the accumulator
-  uint64_t park_full;           // leader: 8 epilogue warps have written Q, K and V^T of the head
+  uint64_t acc_empty;           // leader: 16 epilogue warps have read the accumulator
+  uint64_t park_full;           // leader: 16 epilogue warps have written Q, K and V^T of the head
   uint64_t qk_free;             // per CTA: the head's score MMAs have completed (Q and K may be overwritten)
   uint64_t v_free[2];           // per CTA: the head's P V MMAs have completed (this V^T buffer may be overwritten)
   uint64_t s_full;              // per CTA: scores are in tensor memory
@@ -76,6 +79,61 @@ struct Shared {
 constexpr int kSharedBytes = static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
 constexpr int kSmemBytes = 1024 + kKChunks * kXChunkBytes + kWStages * kWStageBytes + kKParkBytes + 2 * kVtBufBytes + kSharedBytes;
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB a CTA may use");
+
+// Row maximum of the visible raw scores (this thread's row of a 128 x 128 tile), two 32-column loads in flight.
+__device__ __forceinline__ float tile_row_max_pipelined(uint32_t s_addr, const attn_tile::GroupVis& g) {
+  float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  auto fold = [&](const uint32_t (&s)[32], int c0) {
+    if (g.full(c0)) {
+#pragma unroll
+      for (int cc = 0; cc < 32; ++cc) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
+    } else {
+#pragma unroll
+      for (int cc = 0; cc < 32; ++cc)
+        if (c0 + cc >= g.vis_lo && c0 + cc <= g.vis_hi) m[cc & 3] = fmaxf(m[cc & 3], __uint_as_float(s[cc]));
+    }
+  };
+#pragma unroll 1
+  for (int c0 = 0; c0 < kTile; c0 += 64) {
+    const bool skip_a = g.skip(c0), skip_b = g.skip(c0 + 32);       // the same for every lane of the warp
+    uint32_t a[32], b[32];
+    if (!skip_a) tmem_ld32(s_addr + c0, a);
+    if (!skip_b) tmem_ld32(s_addr + c0 + 32, b);
+    if (!skip_a || !skip_b) tmem_ld_wait();
+    if (!skip_a) fold(a, c0);
+    if (!skip_b) fold(b, c0 + 32);
+  }
+  return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
+
+// This thread's 64 output values from tensor memory, scaled and rounded to 32 packed words.
+template <typename VT>
+__device__ __forceinline__ void pack_output_row(uint32_t o_addr, float inv, uint32_t (&w)[32]) {
+#pragma unroll
+  for (int d0 = 0; d0 < kD; d0 += 32) {
+    uint32_t o[32];
+    tmem_ld32(o_addr + d0, o);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      w[d0 / 2 + j] = Pack16<VT>::pack(__uint_as_float(o[2 * j]) * inv, __uint_as_float(o[2 * j + 1]) * inv);
+  }
+}
+// Same for the weighted sum of two partial outputs:  c_a * O_a + c_b * O_b.
+template <typename VT>
+__device__ __forceinline__ void pack_output_row2(uint32_t oa_addr, uint32_t ob_addr, float c_a, float c_b, uint32_t (&w)[32]) {
+#pragma unroll
+  for (int d0 = 0; d0 < kD; d0 += 16) {       // 16 columns of each at a time: the 32 packed words stay live throughout
+    uint32_t oa[16], ob[16];
+    tmem_ld16(oa_addr + d0, oa);
+    tmem_ld16(ob_addr + d0, ob);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[d0 / 2 + j] = Pack16<VT>::pack(fmaf(__uint_as_float(oa[2 * j]), c_a, __uint_as_float(ob[2 * j]) * c_b),
+                                       fmaf(__uint_as_float(oa[2 * j + 1]), c_a, __uint_as_float(ob[2 * j + 1]) * c_b));
+  }
+}
 }  // namespace fused
 
 template <typename VT>
@@ -128,7 +186,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     sh->skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1u : 0u;
     fence_mbar_init();
   }
-  if (warp == 12) {
+  if (warp == kIssueWarp0) {
     tmem_alloc_pair(&sh->tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
@@ -146,7 +204,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
 
   if (skip) {
     // a previous kernel already reported an error through this status word: do nothing
-  } else if (warp == 12) {
+  } else if (warp == kIssueWarp0) {
     // ------------------------------------------------------------ W loads (one thread per CTA)
     if (lane == 0) {
       tma_prefetch_desc(&tmap_w);
@@ -170,7 +228,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         }
       }
     }
-  } else if (warp == 13) {
+  } else if (warp == kIssueWarp0 + 1) {
     // ------------------------------------------------------------ x loads (one thread per CTA)
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
@@ -183,16 +241,23 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         }
       }
     }
-  } else if (warp == 14) {
+  } else if (warp == kIssueWarp0 + 2) {
     // ------------------------------------------------------------ projection MMAs (leader CTA only)
     if (leader && lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int chunk = 0;                 // running count of K chunks issued
       for (int g = 0; g < n_heads_total; ++g) {
         const int n = g >> 3, h = g & 7;
         if (g >= 1) mbar_wait(&sh->acc_empty, static_cast<uint32_t>(g - 1) & 1u, ctl, status, kErrWaitConsumer);
         tc_fence_after_sync();
-        for (int kc = 0; kc < kKChunks; ++kc) {
+        for (int kc = 0; kc < kKChunks; ++kc, ++chunk) {
+          // The tensor core runs MMAs in issue order.  At most two chunks (8 MMAs) of projection are queued, so
+          // that the attention MMAs of the other issuing warp, which sit on the critical path, wait behind
+          // little: chunk c is issued once chunk c - 2 has completed.
+          if (chunk >= 2)
+            mbar_wait(&sh->w_empty[(chunk - 2) % kWStages], static_cast<uint32_t>((chunk - 2) / kWStages) & 1u, ctl, status,
+                      kErrWaitMma);
           if (h == 0) mbar_wait(&sh->x_full[kc], static_cast<uint32_t>(n) & 1u, ctl, status, kErrWaitTma);
           mbar_wait(&sh->w_full[stage], phase, ctl, status, kErrWaitTma);
           tc_fence_after_sync();
@@ -208,7 +273,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         tc_commit_pair(&sh->acc_full, 3);
       }
     }
-  } else if (warp == 15) {
+  } else if (warp == kIssueWarp0 + 3) {
     // ------------------------------------------------------------ attention MMAs (leader CTA only)
     if (leader && lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_f16(2 * kTile, 2 * kTile, 1, 1, 0, 0);                        // bf16 q, k
@@ -242,31 +307,33 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       }
     }
   } else if (warp < kEpiWarps) {
-    // ------------------------------------------------------------ epilogue: one frame row per thread
-    const int lg = warp;
+    // ------------------------------------------------------------ epilogue: two threads per frame row; `half`
+    // selects RoPE pair set 16 half .. 16 half + 15 (dimensions d and d + 32) of q and k, and dimensions
+    // 32 half .. 32 half + 31 of v (which are the rows of CTA `half`'s V^T).
+    const int lg = warp & 3, half = warp >> 2;
     const int row = lg * 32 + lane;
     const int frame = static_cast<int>(rank) * kTile + row;         // also the key index of this row's K and V
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16);
-    float rc[32], rs[32];
+    float rc[16], rs[16];
     auto load_tables = [&](int clip) {
       if (frame < T) {
-        const float4* c4 = reinterpret_cast<const float4*>(cos_tab + clip * cos_bstride + static_cast<long long>(frame) * 64);
-        const float4* s4 = reinterpret_cast<const float4*>(sin_tab + clip * cos_bstride + static_cast<long long>(frame) * 64);
+        const float4* c4 = reinterpret_cast<const float4*>(cos_tab + clip * cos_bstride + static_cast<long long>(frame) * 64 + half * 16);
+        const float4* s4 = reinterpret_cast<const float4*>(sin_tab + clip * cos_bstride + static_cast<long long>(frame) * 64 + half * 16);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           const float4 c = __ldg(c4 + j), sn = __ldg(s4 + j);
           rc[4 * j] = c.x; rc[4 * j + 1] = c.y; rc[4 * j + 2] = c.z; rc[4 * j + 3] = c.w;
           rs[4 * j] = sn.x; rs[4 * j + 1] = sn.y; rs[4 * j + 2] = sn.z; rs[4 * j + 3] = sn.w;
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) { rc[j] = 1.f; rs[j] = 0.f; }
+        for (int j = 0; j < 16; ++j) { rc[j] = 1.f; rs[j] = 0.f; }
       }
     };
     if (cos_bstride == 0) load_tables(0);
     // V^T destinations: dimension d of this key goes to CTA d / 32, row d % 32 of tile key / 64, at byte
     // ((key % 64) / 8 ^ (d % 8)) * 16 + (key % 8) * 2 of the 128-byte row (the 128-byte swizzle).
-    const uint32_t vt_cta[2] = {map_to_cta(smem_u32(smem_vt), 0), map_to_cta(smem_u32(smem_vt), 1)};
+    const uint32_t vt_cta = map_to_cta(smem_u32(smem_vt), static_cast<uint32_t>(half));
     const uint32_t vt_key = static_cast<uint32_t>((frame >> 6) * kVtTileBytes + (frame & 7) * 2);
     const uint32_t vt_chunk = static_cast<uint32_t>((frame & 63) >> 3);
     for (int g = 0; g < n_heads_total; ++g) {
@@ -278,8 +345,8 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       tc_fence_after_sync();
 #pragma unroll
       for (int seg = 0; seg < 2; ++seg) {          // 0 = q -> tensor memory, 1 = k -> shared memory
-#pragma unroll
-        for (int piece = 0; piece < 2; ++piece) {
+        {
+          const int piece = half;
           // 16 columns of the first half of the head and the 16 columns 32 further on: a RoPE pair set
           uint32_t lo[16], hi[16];
           tmem_ld16(t_row + kAccCol + seg * 64 + piece * 16, lo);
@@ -292,7 +359,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const float a = __uint_as_float(lo[d + e]), b = __uint_as_float(hi[d + e]);
-              const float c = rc[piece * 16 + d + e], sn = rs[piece * 16 + d + e];
+              const float c = rc[d + e], sn = rs[d + e];
               o_lo[e] = a * c - b * sn;
               o_hi[e] = b * c + a * sn;
             }
@@ -314,21 +381,22 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       if (g >= 2) mbar_wait(&sh->v_free[g & 1], (static_cast<uint32_t>(g >> 1) & 1u) ^ 1u, ctl, status, kErrWaitMma);
       const uint32_t vt_buf = static_cast<uint32_t>((g & 1) * kVtBufBytes) + vt_key;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q2 = 0; q2 < 2; ++q2) {
+        const int q4 = 2 * half + q2;
         uint32_t vv[16];
         tmem_ld16(t_row + kAccCol + 128 + q4 * 16, vv);
         tmem_ld_wait();
-        if (q4 == 3) {
+        if (q2 == 1) {
           // last read of the accumulator: hand it back before the stores (the loads have completed, so the
           // arrival needs no release ordering)
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_l);
         }
-        const uint32_t dst = vt_cta[q4 >> 1] + vt_buf;
+        const uint32_t dst = vt_cta + vt_buf;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int dr = (q4 & 1) * 16 + j;                        // row of the V^T tile
+          const int dr = q2 * 16 + j;                              // row of the V^T tile
           const uint32_t v16 = Pack16<VT>::pack(__uint_as_float(vv[j]), 0.f) & 0xFFFFu;
           st_shared_cluster_u16(dst + static_cast<uint32_t>(dr * 128) + ((vt_chunk ^ static_cast<uint32_t>(dr & 7)) << 4),
                                 static_cast<uint16_t>(v16));
@@ -340,9 +408,9 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(park_full_l);
     }
-  } else if (!(warp >= 8 && leader)) {
+  } else if (!(warp >= kTeamWarp0 + 4 && leader)) {
     // ------------------------------------------------------------ softmax teams (team B only where rows see keys >= 128)
-    const int team = (warp - 4) >> 2;           // 0: keys 0-127, 1: keys 128-255
+    const int team = (warp - kTeamWarp0) >> 2;  // 0: keys 0-127, 1: keys 128-255
     const int lg = warp & 3;
     const int row = lg * 32 + lane;
     const int w_row0 = static_cast<int>(rank) * kTile + lg * 32;
@@ -368,7 +436,9 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive_cluster(p_full_l);
+        // P lives in tensor memory and its stores have completed (tcgen05.wait::st), so the arrival orders
+        // nothing; the release form would also wait for this thread's output stores still in flight.
+        mbar_arrive_cluster_relaxed(p_full_l);
         if (publishes) mbar_arrive(&sh->xl_full);
       }
       if (publishes) continue;                 // its O stays in tensor memory until team B has combined it
@@ -378,6 +448,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       tc_fence_after_sync();
       const int clip = pair + (g >> 3) * n_pairs, h = g & 7;
       uint16_t* dst = i < T ? out + (static_cast<long long>(clip) * T + i) * 512 + h * kD : nullptr;
+      uint32_t packed[32];
       if (combines) {
         mbar_wait(&sh->xl_full, ph, ctl, status, kErrWaitConsumer);
         const float m1 = sh->xs[row][0], l1 = sh->xs[row][1];
@@ -385,13 +456,20 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const float a2 = ex2_approx(m_use - m);
         const float a1 = (m1 == -INFINITY) ? 0.f : ex2_approx(m1 - m);
         const float inv = 1.f / (a1 * l1 + a2 * l_row);
-        store_output_row2<VT>(s_addr + kOOff, sa_addr + kOOff, dst, a2 * inv, a1 * inv);
+        pack_output_row2<VT>(s_addr + kOOff, sa_addr + kOOff, a2 * inv, a1 * inv, packed);
       } else {
-        store_output_row<VT>(s_addr + kOOff, dst, 1.f / l_row);
+        pack_output_row<VT>(s_addr + kOOff, 1.f / l_row, packed);
       }
+      // The score columns are free as soon as O is in registers: the next head's scores do not wait for the
+      // global stores.
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(slot_free_l);
+      if (dst != nullptr) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          reinterpret_cast<uint4*>(dst)[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
     }
   }
 
@@ -400,7 +478,7 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
   __syncthreads();
   if (ctl->abort) __nanosleep(20000);
   cluster_sync_all();
-  if (warp == 12) {
+  if (warp == kIssueWarp0) {
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
