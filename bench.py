@@ -37,9 +37,11 @@ if ROOT not in sys.path:
 
 CLIPS, FRAMES, LAYERS, HIDDEN, WINDOW = 512, 250, 16, 512, 250
 QKV_FLOP_PER_FRAME = 2 * 512 * 1536
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
-# profiles/, taken on a 256-clip case and scaled to this workload's 512 clips (traffic grows with frames).
-NCU_TRAFFIC_BYTES = {"qkv_rope_gemm_kernel": 2 * 217.5e6, "band_attn_prefill_kernel": 2 * 237.0e6}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel.  ncu cannot run inside this
+# script, so these come from the captures summarised under profiles/ (same kernels, a 256-clip case: traffic grows in
+# proportion to the clips) scaled by 2 to this workload's 512 clips; the line says so in `traffic_source`.
+NCU_TRAFFIC_BYTES_256_CLIPS = {"qkv_rope_gemm_kernel": 217.5e6, "band_attn_clip_kernel": 237.0e6}
+DTYPE = "bf16 x, W, q, k / fp16 v, p, out / fp32 accumulate"
 
 
 def pairs(t: int, window: int = WINDOW) -> int:
@@ -207,7 +209,8 @@ def run_reference(args) -> None:
 def config_dict() -> dict:
     return {"workload": "batched prefill (benchmark config 3): QKV projection + RoPE + banded causal attention, "
                         "16 layers", "clips_per_gpu": CLIPS, "frames": FRAMES, "layers": LAYERS, "window": WINDOW,
-            "heads": 8, "head_dim": 64, "l2": "inputs larger than L2: each layer streams 655 MB (x, q, k, v, out)"}
+            "heads": 8, "head_dim": 64,
+            "l2": "inputs larger than L2: x and out of one layer are 262 MB (the two-kernel path adds 393 MB of q, k, v)"}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -235,7 +238,7 @@ def pin_to_gpu_numa_node(gpu_index: int) -> None:
 def run_ours(args) -> None:
     import torch.distributed as dist
     import fast_mimi_b200 as fm
-    from fast_mimi_b200 import ops
+    from fast_mimi_b200 import ops, sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -275,16 +278,20 @@ def run_ours(args) -> None:
     status = ops.new_status(dev)
     stream = torch.cuda.current_stream()
 
-    def step(events=None, xin=None, outbuf=None):
+    def step(events=None, xin=None, outbuf=None, clips=CLIPS):
+        """One pass of the 16 layers: projection + RoPE kernel, then the whole-clip attention kernel (what the public
+        entry point for a cache-free call, ops.attention_prefill, runs; issued as its two halves here so that each
+        kernel can be timed with events on the launching stream)."""
         xin = x if xin is None else xin
         outbuf = out if outbuf is None else outbuf
+        ws_ = (q[:clips], k[:clips], v[:clips])
         for l in range(LAYERS):
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record(stream)
-            ops.qkv_rope(xin, ws[l], cos, sin, out=(q, k, v), status=status)
+            ops.qkv_rope(xin[:clips], ws[l], cos, sin, out=ws_, status=status)
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record(stream)
-            ops.band_attention_prefill(q, k, v, window=WINDOW, scale=0.125, out=outbuf, status=status)
+            ops.band_attention_prefill(*ws_, window=WINDOW, scale=0.125, out=outbuf[:clips], status=status)
             if events is not None:
                 e2 = torch.cuda.Event(enable_timing=True); e2.record(stream)
                 events.append((e0, e1, e2))
@@ -302,10 +309,47 @@ def run_ours(args) -> None:
         stop.record(stream)
         barrier()
     ms_total = start.elapsed_time(stop)
-    if ops.read_status(status) != 0:
-        raise SystemExit(f"a bounded device wait timed out (status {ops.read_status(status)})")
+    ops.check_status(status=status)
     gemm_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in events)
     attn_ms = statistics.mean(b.elapsed_time(c) for _, b, c in events)
+
+    # ---- parity of the timed configuration's own output -------------------------------------
+    # The buffers of the timed run, full-size launches: every layer's result for the first clips against the CPU
+    # oracle on the same values (relative L2, tolerance 2e-3 as in tests/).
+    parity = None
+    if rank == 0 and not args.no_cpu:
+        from oracle import mimi_attention_oracle as O
+        n_par = 8
+        xs_cpu = x[:n_par].float().cpu()
+        cos_c, sin_c = O.rope_tables(torch.arange(FRAMES))
+        worst = 0.0
+        worst_fused = 0.0
+        out_f = torch.empty_like(out)
+        for l in range(LAYERS):
+            ops.attention_prefill(x, ws[l], cos, sin, window=WINDOW, scale=0.125, workspace=(q, k, v), out=out, status=status)
+            ops.attention_fused(x, ws[l], cos, sin, window=WINDOW, scale=0.125, out=out_f, status=status)
+            got = out[:n_par].float().cpu()
+            qc, kc, vc = O.qkv_project(xs_cpu, *ws[l].float().cpu().chunk(3, 0))
+            qc, kc = O.apply_rope(qc, kc, cos_c, sin_c)
+            want = O.band_attention(qc, kc, vc).transpose(1, 2).reshape(n_par, FRAMES, HIDDEN)
+            worst = max(worst, O.rel_l2(got, want))
+            worst_fused = max(worst_fused, O.rel_l2(out_f[:n_par].float().cpu(), want))
+        del out_f
+        parity = {"rel_l2_max": worst, "clips": n_par, "layers": LAYERS, "tolerance": 2e-3, "ok": worst <= 2e-3,
+                  "rel_l2_max_fused_kernel": worst_fused,
+                  "what": "output of the full-size launches of the timed configuration vs the CPU oracle"}
+
+    # ---- the same layer as ONE kernel (projection + RoPE + attention, q / k / v never in memory); not in the step ----
+    fused_events: list = []
+    for it in range(3 + 8):
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        ops.attention_fused(x, ws[it % LAYERS], cos, sin, window=WINDOW, scale=0.125, out=out, status=status)
+        e1.record(stream)
+        if it >= 3:
+            fused_events.append((e0, e1))
+    torch.cuda.synchronize()
+    fused_ms = statistics.mean(a.elapsed_time(b) for a, b in fused_events)
 
     # ---- end to end: pinned host input -> device -> 16 layers -> host --------------------------
     # Every step copies its batch in from pinned memory and its result out; the copies of neighbouring
@@ -317,7 +361,7 @@ def run_ours(args) -> None:
     out_devs = [out, torch.empty_like(out)]
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
-    def e2e_run(n_steps):
+    def e2e_run(n_steps, compute=True):
         in_ready = [None, None]; computed = [None, None]; copied_out = [None, None]
         for i in range(n_steps):
             b = i & 1
@@ -329,7 +373,8 @@ def run_ours(args) -> None:
             stream.wait_event(in_ready[b])
             if copied_out[b] is not None:
                 stream.wait_event(copied_out[b])            # out_devs[b] has left for the host
-            step(xin=x_devs[b], outbuf=out_devs[b])
+            if compute:
+                step(xin=x_devs[b], outbuf=out_devs[b])
             computed[b] = torch.cuda.Event(); computed[b].record(stream)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(computed[b])
@@ -347,6 +392,32 @@ def run_ours(args) -> None:
     t2.record(stream)
     barrier()
     ms_e2e = s2.elapsed_time(t2)
+    # The same loop without the kernels: what the host side alone can carry (all ranks at once).
+    e2e_run(2, compute=False)
+    barrier()
+    s3 = torch.cuda.Event(enable_timing=True); t3 = torch.cuda.Event(enable_timing=True)
+    s3.record(stream)
+    e2e_run(10, compute=False)
+    t3.record(stream)
+    barrier()
+    ms_copy = s3.elapsed_time(t3) / 10
+
+    # ---- strong scaling: the batch of benchmark config 3 (512 clips in total) split over the ranks -----------
+    lo, hi = sharding.shard_bounds(CLIPS, world, rank)
+    n_strong = hi - lo
+    for _ in range(3):
+        step(clips=n_strong)
+    barrier()
+    s4 = torch.cuda.Event(enable_timing=True); t4 = torch.cuda.Event(enable_timing=True)
+    s4.record(stream)
+    for _ in range(args.steps):
+        step(clips=n_strong)
+    t4.record(stream)
+    barrier()
+    ms_strong = s4.elapsed_time(t4) / args.steps
+
+    # ---- long clips (benchmark config 4): 16 clips of 2500 frames split over the ranks ------------------------
+    longclip = bench_longclip(dev, stream, peaks, world, rank)
 
     # ---- streaming decode (benchmark config 5) on a full ring ----------------------------------
     decode = None
@@ -367,6 +438,7 @@ def run_ours(args) -> None:
         ops.out_proj(out, w_o, layer_scale=scale_o, residual=resid, out=y, status=status)
     o1.record(stream)
     torch.cuda.synchronize()
+    ops.check_status(status=status)
     oproj_ms = o0.elapsed_time(o1) / 10
     oproj_bytes = 3 * out.numel() * 2
     out_proj = {"kernel": "qkv_rope_gemm_kernel (output projection + layer scale + residual)", "ms": oproj_ms,
@@ -374,10 +446,10 @@ def run_ours(args) -> None:
                 "gbs": oproj_bytes / (oproj_ms / 1e3) / 1e9, "frac_hbm": oproj_bytes / (oproj_ms / 1e3) / 1e9 / peaks["hbm_gbs"],
                 "note": "next step after the timed path; not included in value or e2e"}
 
-    times = torch.tensor([ms_total, ms_e2e, gemm_ms, attn_ms], device=dev, dtype=torch.float64)
+    times = torch.tensor([ms_total, ms_e2e, fused_ms, gemm_ms, attn_ms, ms_copy, ms_strong], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e, gemm_ms, attn_ms = times.tolist()
+    ms_total, ms_e2e, fused_ms, gemm_ms, attn_ms, ms_copy, ms_strong = times.tolist()
     frames_per_step = CLIPS * FRAMES * LAYERS * world
     ms_per_step = ms_total / args.steps
     value = frames_per_step / (ms_per_step / 1e3)
@@ -387,29 +459,56 @@ def run_ours(args) -> None:
     gemm_flop = rows * QKV_FLOP_PER_FRAME
     attn_flop = CLIPS * 2048 * pairs(FRAMES)
     attn_bytes = 4 * rows * HIDDEN * 2
+    fused_bytes = 2 * rows * HIDDEN * 2
+    fused_tf = (gemm_flop + attn_flop) / (fused_ms / 1e3) / 1e12
     gemm_tf = gemm_flop / (gemm_ms / 1e3) / 1e12
     attn_gbs = attn_bytes / (attn_ms / 1e3) / 1e9
+
+    def traffic(name):
+        t = NCU_TRAFFIC_BYTES_256_CLIPS.get(name)
+        return None if t is None else 2 * t
+
     kernels = [
-        {"kernel": "qkv_rope_gemm_kernel", "ms": gemm_ms, "share": gemm_ms / (gemm_ms + attn_ms), "bound": "tensor",
-         "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": gemm_tf / peaks["bf16_tflops"]},
-        {"kernel": "band_attn_prefill_kernel", "ms": attn_ms, "share": attn_ms / (gemm_ms + attn_ms), "bound": "hbm",
-         "achieved": attn_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn_gbs / peaks["hbm_gbs"],
-         "tensor_tflops": attn_flop / (attn_ms / 1e3) / 1e12},
+        {"kernel": "qkv_rope_gemm_kernel", "in_step": True, "ms": gemm_ms, "share": gemm_ms / (gemm_ms + attn_ms),
+         "bound": "tensor", "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+         "frac": gemm_tf / peaks["bf16_tflops"], "frac_sustained": gemm_tf / peaks["bf16_tflops_sustained"],
+         "algorithmic_flop": gemm_flop},
+        {"kernel": "band_attn_clip_kernel", "in_step": True, "ms": attn_ms, "share": attn_ms / (gemm_ms + attn_ms),
+         "bound": "hbm", "achieved": attn_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn_gbs / peaks["hbm_gbs"],
+         "frac_sustained": attn_gbs / peaks["hbm_gbs"], "tensor_tflops": attn_flop / (attn_ms / 1e3) / 1e12,
+         "algorithmic_bytes": attn_bytes},
+        {"kernel": "attn_fused_clip_kernel", "in_step": False, "ms": fused_ms, "bound": "tensor",
+         "achieved": fused_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fused_tf / peaks["bf16_tflops"],
+         "frac_sustained": fused_tf / peaks["bf16_tflops_sustained"],
+         "gbs": fused_bytes / (fused_ms / 1e3) / 1e9, "algorithmic_flop": gemm_flop + attn_flop, "algorithmic_bytes": fused_bytes,
+         "note": "one kernel for the whole layer call (x in, attention out, 2.5x fewer HBM bytes); timed after the step, "
+                 "not part of it: the two kernels above are the faster way today"},
     ]
-    top = max(kernels, key=lambda d: d["ms"])
+    top = max(kernels[:2], key=lambda d: d["ms"])
     roofline = {"bound": top["bound"], "achieved": top["achieved"], "peak": top["peak"], "unit": top["unit"],
-                "frac": top["frac"], "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]), "kernel": top["kernel"],
-                "peak_source": f"{peaks['source']} (burst figure)", "avg_launch_ms": top["ms"]}
+                "frac": top["frac"], "frac_sustained": top["frac_sustained"], "traffic": traffic(top["kernel"]),
+                "traffic_source": "profiles/ (ncu capture of a 256-clip launch, scaled x2 by the clips processed)",
+                "kernel": top["kernel"], "peak_source": f"{peaks['source']} (burst figure; frac_sustained uses the sustained one)",
+                "avg_launch_ms": top["ms"]}
 
     if rank == 0:
         cpu = time_cpu_baseline() if world == 1 and not args.no_cpu else None
+        h2d, d2h = x.numel() * 2, out.numel() * 2
         line = {
             "metric": "attention frames/s", "value": value, "unit": "frames/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(),
-            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": x.numel() * 2,
-                    "d2h_bytes_per_step": out.numel() * 2, "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * LAYERS * 2, "roofline": roofline, "kernels": kernels,
+            "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": config_dict(),
+            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": args.steps * LAYERS * 2, "roofline": roofline, "kernels": kernels, "parity": parity,
+            "host_copy": {"ms_per_step": ms_copy, "gbs_per_gpu": (h2d + d2h) / (ms_copy / 1e3) / 1e9,
+                          "gbs_all_gpus": world * (h2d + d2h) / (ms_copy / 1e3) / 1e9,
+                          "what": "the e2e loop's pinned-host copies alone (no kernels), all ranks at once, max over ranks: "
+                                  "the ceiling the host side puts on e2e"},
+            "strong": {"scaling": "strong", "clips_total": CLIPS, "clips_per_gpu": n_strong, "ms_per_step": ms_strong,
+                       "value": CLIPS * FRAMES * LAYERS / (ms_strong / 1e3), "unit": "frames/s",
+                       "what": "benchmark config 3 as stated: 512 clips in total, split evenly over the GPUs"},
+            "longclip": longclip,
             "clocks": clocks.summary(), "cpu_baseline": cpu, "decode": decode, "out_proj": out_proj,
             "step_tflops": (gemm_flop + attn_flop) * LAYERS / (ms_per_step / 1e3) / 1e12,
         }
@@ -421,6 +520,47 @@ def run_ours(args) -> None:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_longclip(dev, stream, peaks, world, rank, clips_total: int = 16, T: int = 2500, steps: int = 20) -> dict:
+    """Benchmark config 4 (banded attention alone on 16 clips of 2500 frames, rotated BF16 q, k / FP16 v resident),
+    the clips split evenly over the ranks; three input sets in rotation so that none survives in L2."""
+    import torch.distributed as dist
+    from fast_mimi_b200 import ops, sharding
+    lo, hi = sharding.shard_bounds(clips_total, world, rank)
+    B = hi - lo
+    g = torch.Generator(device=dev).manual_seed(11 + rank)
+    n_sets = 3 if world == 1 else 3 * world       # per-rank inputs shrink with the split: keep the rotation above L2
+    sets = []
+    for _ in range(n_sets):
+        sets.append(((torch.randn(B, T, 512, device=dev, generator=g) / 8).bfloat16(),
+                     (torch.randn(B, T, 512, device=dev, generator=g) / 8).bfloat16(),
+                     (torch.randn(B, T, 512, device=dev, generator=g) / 8).half()))
+    out = torch.empty_like(sets[0][2])
+    for i in range(3):
+        ops.band_attention_prefill(*sets[i % n_sets], window=WINDOW, out=out)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for i in range(steps):
+        ops.band_attention_prefill(*sets[i % n_sets], window=WINDOW, out=out)
+    b.record(stream)
+    torch.cuda.synchronize()
+    ms = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms)
+    nbytes = 4 * clips_total * T * 512 * 2
+    gbs = nbytes / (ms / 1e3) / 1e9
+    del sets
+    torch.cuda.empty_cache()
+    return {"workload": "long-clip banded attention (benchmark config 4), one layer call", "clips_total": clips_total,
+            "clips_per_gpu": B, "frames": T, "ms_per_call": ms, "value": clips_total * T / (ms / 1e3), "unit": "frames/s",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s",
+                         "frac": gbs / (peaks["hbm_gbs"] * world), "kernel": "band_attn_long_kernel",
+                         "tensor_tflops": clips_total * 2048 * pairs(T) / (ms / 1e3) / 1e12}}
 
 
 def bench_decode(dev, stream, peaks, world, rank, streams: int = 4096, layers: int = 8, steps: int = 20) -> dict:
@@ -497,6 +637,20 @@ def profile_case(which: str) -> None:
         cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)
         for _ in range(4):
             ops.attention_prefill(x, w, cos, sin)
+    elif which == "fused":
+        x = torch.randn(256, FRAMES, HIDDEN, device=dev, generator=g).bfloat16()
+        cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)
+        for _ in range(4):
+            ops.attention_fused(x, w, cos, sin)
+    elif which == "chunk":
+        # 512 streams, 64 new frames on top of full rings: the offset-key attention kernel and the two ring copies
+        ring = fm.MimiKVRing(1, 512, WINDOW, device=dev)
+        ring.ring_k.copy_((torch.randn(ring.ring_k.shape, device=dev, generator=g) / 2).bfloat16())
+        ring.ring_v.copy_((torch.randn(ring.ring_v.shape, device=dev, generator=g) / 2).half())
+        xs = torch.randn(512, 64, HIDDEN, device=dev, generator=g).bfloat16()
+        cos = torch.ones(1, 64, 64, device=dev); sin = torch.zeros(1, 64, 64, device=dev)
+        for i in range(3):
+            ops.attention_chunk(xs, w, cos, sin, ring.ring_k[0], ring.ring_v[0], 300 + 64 * i)
     elif which == "layer":
         layer = fm.MimiTransformerLayerB200().to(dev)
         x = torch.randn(256, FRAMES, HIDDEN, device=dev, generator=g)
@@ -541,23 +695,73 @@ def run_extra_workload(args) -> None:
     if args.workload == "stack":
         run_stack(args, dev, peaks, stream, g)
         return
+    if args.workload == "streamlayer":
+        # config 5's step through WHOLE transformer layers (LayerNorms, projections, ring decode, MLP; all on this
+        # library's kernels): 4096 streams x 8 layers, one new frame per stream, full 250-slot rings
+        S, L = 4096, 8
+        layers = [fm.MimiTransformerLayerB200(layer_idx=l).to(dev) for l in range(L)]
+        ring = fm.MimiKVRing(L, S, WINDOW, device=dev)
+        ring.ring_k.copy_((torch.randn(ring.ring_k.shape[1:], device=dev, generator=g) / 2).bfloat16().expand_as(ring.ring_k))
+        ring.ring_v.copy_((torch.randn(ring.ring_v.shape[1:], device=dev, generator=g) / 2).half().expand_as(ring.ring_v))
+        ring._cumulative_lengths = [WINDOW] * L
+        x = torch.randn(S, 1, HIDDEN, device=dev, generator=g)
+
+        def one_step(pos):
+            cs = fm.rope_tables(torch.tensor([[pos]], device=dev))
+            h = x
+            with torch.no_grad():
+                for layer in layers:
+                    h, _ = layer(h, None, ring, cs, False)
+            return h
+
+        n_warm = max(args.warmup, 3)
+        for i in range(n_warm):
+            one_step(WINDOW + i)
+        torch.cuda.synchronize()
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        steps = min(args.steps, 50)
+        a.record(stream)
+        for i in range(steps):
+            one_step(WINDOW + n_warm + i)
+        b.record(stream)
+        torch.cuda.synchronize()
+        fm.check_status()
+        ms = a.elapsed_time(b) / steps
+        ring_bytes = S * L * (2 * WINDOW * 512 * 2)
+        print(json.dumps({"metric": "transformer-layer frames/s (streaming)", "value": S * L / (ms / 1e3), "unit": "frames/s",
+                          "n_gpus": 1, "steps": steps, "ms_per_step": ms, "dtype": "fp16 operands, bf16 / fp16 ring, fp32 residual stream",
+                          "data": "synthetic",
+                          "config": {"workload": "streaming decode through whole transformer layers (benchmark config 5's step)",
+                                     "streams": S, "layers": L, "ring_slots": WINDOW},
+                          "ring_gbs": ring_bytes / (ms / 1e3) / 1e9, "frac_hbm_ring_only": ring_bytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"]}))
+        return
     if args.workload == "rvq":
         # the quantiser that follows the encoder transformer: config 3's batch after the stride-2 downsample,
         # 512 clips x 125 frames = 64 000 vectors of 256 dimensions, 8 codebooks of 2048 entries
         rows, layers = CLIPS * FRAMES // 2, 8
         books = ops.RVQCodebooks(torch.randn(layers, 2048, 256, device=dev, generator=g)
                                  * (0.6 ** torch.arange(layers, device=dev, dtype=torch.float32))[:, None, None])
-        x = torch.randn(rows, 256, device=dev, generator=g) * 1.5
+        # embeddings [rows, 512] -> the quantiser's 1 x 1 input projection (512 -> 256, split-precision tensor-core
+        # product) -> eight layers of search; the projection is inside the timed region
+        emb = torch.randn(rows, HIDDEN, device=dev, generator=g) * 1.5
+        proj = ops.split_half((torch.randn(256, HIDDEN, device=dev, generator=g) / HIDDEN ** 0.5).contiguous())
+        x = ops.linear_split(emb, proj)
         for _ in range(max(args.warmup, 3)):
-            codes, cand = ops.rvq_encode(x, books, return_candidates=True)
+            codes, cand = ops.rvq_encode(ops.linear_split(emb, proj), books, return_candidates=True)
         torch.cuda.synchronize()
-        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+        a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True); c = torch.cuda.Event(enable_timing=True)
+        ms_proj = 0.0
         a.record(stream)
         for _ in range(args.steps):
-            ops.rvq_encode(x, books)
+            ops.rvq_encode(ops.linear_split(emb, proj), books)
         b.record(stream)
+        for _ in range(args.steps):
+            ops.linear_split(emb, proj)
+        c.record(stream)
         torch.cuda.synchronize()
+        ops.check_status(dev)
         ms = a.elapsed_time(b) / args.steps
+        ms_proj = b.elapsed_time(c) / args.steps
         flop = rows * layers * 2 * 2048 * 256
         nbytes = rows * layers * (2 * 2048 * 2 + 256 * (2 + 4 + 4 + 2))     # FP16 scores written + read, residual in both types
         print(json.dumps({"metric": "quantised vectors/s", "value": rows / (ms / 1e3), "unit": "vectors/s", "n_gpus": 1,
@@ -566,6 +770,7 @@ def run_extra_workload(args) -> None:
                                      "vectors": rows, "layers": layers},
                           "tensor_tflops": flop / (ms / 1e3) / 1e12, "gbs": nbytes / (ms / 1e3) / 1e9,
                           "frac_hbm": nbytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"],
+                          "input_projection_ms": ms_proj,
                           "exact_evaluations_per_vector_layer": float(cand.float().mean())}))
         return
     if args.workload == "longclip":
@@ -615,11 +820,15 @@ def run_extra_workload(args) -> None:
               for j in range(4)] for l in range(L)]
     cos3, sin3 = cos.view(STEPS, 1, 1, 64), sin.view(STEPS, 1, 1, 64)
 
-    def run_all():
+    PARITY_STEPS, PARITY_LAYERS, PARITY_STREAMS = (0, 249, 250, 499), (0, L - 1), 32
+
+    def run_all(capture=None):
         for t in range(STEPS):
             c, s_ = cos3[t], sin3[t]
             for l in range(L):
                 plans[l][(t + l) & 3].step(t, c, s_)
+                if capture is not None and t in PARITY_STEPS and l in PARITY_LAYERS:
+                    capture[(t, l)] = out[:PARITY_STREAMS].clone()
 
     run_all()                      # warm-up pass (the ring is simply overwritten by the timed pass)
     torch.cuda.synchronize()
@@ -628,8 +837,29 @@ def run_extra_workload(args) -> None:
     run_all()
     b.record(stream)
     torch.cuda.synchronize()
-    assert ops.read_status(status) == 0
+    ops.check_status(status=status)
     ms = a.elapsed_time(b)
+    # Parity of this workload's own steps (an untimed third pass captures them): the first streams at the first
+    # step, the last step of the fill, the first wrapped step and the last step, first and last layer, against the
+    # CPU oracle driven through the same 500 steps with the reference's concatenate-and-crop cache.
+    parity = None
+    if not args.no_cpu:
+        from oracle import mimi_attention_oracle as O
+        got: dict = {}
+        run_all(got)
+        torch.cuda.synchronize()
+        eye = torch.eye(HIDDEN)
+        worst = 0.0
+        for l in PARITY_LAYERS:
+            wq, wk, wv = ws[l].float().cpu().chunk(3, 0)
+            cache = O.KVCacheOracle()
+            xs_cpu = [x_[:PARITY_STREAMS].float().cpu() for x_ in xs]
+            for t in range(STEPS):
+                want = O.attention_forward(xs_cpu[(t + l) & 3][:, None], wq, wk, wv, eye, cache=cache)
+                if t in PARITY_STEPS:
+                    worst = max(worst, O.rel_l2(got[(t, l)].cpu(), want.view(PARITY_STREAMS, HIDDEN)))
+        parity = {"rel_l2_max": worst, "streams": PARITY_STREAMS, "steps": list(PARITY_STEPS), "layers": list(PARITY_LAYERS),
+                  "tolerance": 2e-3, "ok": worst <= 2e-3}
     rows = sum(min(t + 1, WINDOW) for t in range(STEPS))
     nbytes = S * L * (rows * 2 * 512 * 2 + STEPS * (2048 + 1024 + 2048)) + STEPS * L * 1536 * 512 * 2
     gbs = nbytes / (ms / 1e3) / 1e9
@@ -639,7 +869,7 @@ def run_extra_workload(args) -> None:
                                  "streams": S, "layers": L, "ring_slots": WINDOW, "ring_gb": ring.bytes() / 1e9},
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                    "frac": gbs / peaks["hbm_gbs"], "kernel": "qkv_rope_gemm_kernel + ring_decode_attn_kernel",
-                                   "algorithmic_bytes": nbytes}}))
+                                   "algorithmic_bytes": nbytes}, "parity": parity}))
 
 
 def run_stack(args, dev, peaks, stream, g) -> None:
@@ -730,8 +960,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the streaming-decode measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle baseline")
-    ap.add_argument("--profile-case", choices=["prefill", "decode", "layer", "longclip", "rvq"], help="run a small case for ncu and exit")
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "stack", "rvq"],
+    ap.add_argument("--profile-case", choices=["prefill", "fused", "chunk", "decode", "layer", "longclip", "rvq"],
+                    help="run a small case for ncu and exit")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "longclip", "stream", "streamlayer", "stack", "rvq"],
                     help="prefill = headline (config 3); longclip / stream = configs 4 / 5, stack = whole transformer layers, rvq = the quantiser after the encoder transformer; one extra JSON line each")
     args = ap.parse_args()
     if args.profile_case:

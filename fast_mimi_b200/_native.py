@@ -22,6 +22,8 @@ SIGNATURES: dict[str, list] = {
     "fm_linear_f16": [_P, _P, _P, _P, _P, _LL, _I, _I, _I, _I, _I, _P, _P],
     "fm_layernorm_f16": [_P, _I, _P, _P, _F, _P, _I, _LL, _P],
     "fm_rvq_select_f32": [_P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _F, _F, _P, _P],
+    "fm_conv_rows_split": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fm_split_half": [_P, _P, _P, _LL, _P],
     "fm_rvq_to_half": [_P, _P, _LL, _P],
     "fm_rvq_decode_f32": [_P, _P, _P, _LL, _I, _I, _P, _P],
     "fm_band_attn_prefill_bf16": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
@@ -34,6 +36,7 @@ SIGNATURES: dict[str, list] = {
     "fm_band_attn_fp32_verify": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     "fm_linear_fp32_verify": [_P, _P, _P, _I, _I, _I, _P],
     "fm_rope_fp32_verify": [_P, _P, _P, _I, _I, _I, _I, _LL, _P],
+    "fm_selftest_wait_timeout": [_P, _I, _P, _P],
     "fm_read_status": [_P, _P],
 }
 

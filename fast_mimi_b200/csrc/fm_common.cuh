@@ -96,8 +96,8 @@ struct CtaCtl {
 };
 
 // Bounded wait.  Returns false if the CTA is (or becomes) aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaCtl* ctl, int* status,
-                                          int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, CtaCtl* ctl, int* status, int code,
+                                                unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -105,13 +105,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaCtl
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (ctl->abort) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         ctl->abort = 1;
         if (status != nullptr) atomicMax(status, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, CtaCtl* ctl, int* status, int code) {
+  return mbar_wait_limit(bar, parity, ctl, status, code, kWaitLimitNs);
 }
 
 // Same wait with cluster-scope acquire: for a barrier whose arrivals come from the other CTA of a pair and
@@ -244,6 +247,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+// Same shape, 8 and 4 columns.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
 }
 // Store 16 consecutive 32-bit columns of this thread's TMEM row (32 lanes x 16 columns per warp).
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {

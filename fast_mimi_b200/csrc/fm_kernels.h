@@ -62,6 +62,12 @@ int launch_layernorm512(const void* x, int x_dtype, const float* weight, const f
 int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, const float* codebook, float* resid, void* resid16,
                       long long* codes, int* n_candidates, long long rows, int n_codes, float e_max, float tau_rel,
                       int* status, cudaStream_t st);
+// Rows of a strided causal convolution with replicate padding, gathered from frame-major FP32 activations and split
+// into FP16 hi + lo parts: [B * ceil(T / stride), kernel * C] (fm_downsample.cu).
+int launch_conv_rows_split(const float* x, void* hi, void* lo, int B, int T, int C, int kernel, int stride,
+                           cudaStream_t st);
+int launch_wait_timeout_selftest(int* status, int limit_us, int* observed, cudaStream_t st);
+int launch_split_half(const float* x, void* hi, void* lo, long long n, cudaStream_t st);
 int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st);
 int launch_rvq_decode(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
                       int n_codes, int* bad_code, cudaStream_t st);

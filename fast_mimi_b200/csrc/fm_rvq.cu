@@ -167,6 +167,27 @@ rvq_to_half_kernel(const float* __restrict__ x, uint16_t* __restrict__ y, long l
   }
 }
 
+// x = hi + lo with both parts in FP16 (hi = round(x), lo = round(x - hi)): 22 significant bits, enough for an
+// FP32-grade product on the FP16 tensor core as  hi W_hi + hi W_lo + lo W_hi  with FP32 accumulation.
+__global__ void __launch_bounds__(256)
+split_half_kernel(const float* __restrict__ x, uint16_t* __restrict__ hi, uint16_t* __restrict__ lo, long long n8) {
+  const long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = i0; i < n8; i += stride) {
+    const float4 a = reinterpret_cast<const float4*>(x)[2 * i], b = reinterpret_cast<const float4*>(x)[2 * i + 1];
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      h[e] = Pack16<__half>::pack(v[2 * e], v[2 * e + 1]);
+      const float2 back = Pack16<__half>::unpack(h[e]);
+      l[e] = Pack16<__half>::pack(v[2 * e] - back.x, v[2 * e + 1] - back.y);
+    }
+    reinterpret_cast<uint4*>(hi)[i] = make_uint4(h[0], h[1], h[2], h[3]);
+    reinterpret_cast<uint4*>(lo)[i] = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+
 // out[row, :] = ((0 + E_0[c_0]) + E_1[c_1]) + ...  in FP32, layers left to right.
 __global__ void __launch_bounds__(256)
 rvq_decode_kernel(const long long* __restrict__ codes, const float* __restrict__ codebooks, float* __restrict__ out,
@@ -228,6 +249,15 @@ int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st)
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) return -3;
   const long long n8 = rows * (rvq::kDim / 8);
   rvq_to_half_kernel<<<grid_for((n8 + 255) / 256, 8), 256, 0, st>>>(x, static_cast<uint16_t*>(y), n8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_split_half(const float* x, void* hi, void* lo, long long n, cudaStream_t st) {
+  if (n < 0 || n % 8 != 0) return -1;
+  if (n == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 15u) return -3;
+  const long long n8 = n / 8;
+  split_half_kernel<<<grid_for((n8 + 255) / 256, 8), 256, 0, st>>>(x, static_cast<uint16_t*>(hi), static_cast<uint16_t*>(lo), n8);
   return static_cast<int>(cudaGetLastError());
 }
 

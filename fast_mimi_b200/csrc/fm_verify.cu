@@ -157,4 +157,35 @@ int launch_band_attn_fp32(const float* q, const float* k, const float* v, float*
   return static_cast<int>(cudaGetLastError());
 }
 
+// Self-test of the bounded-wait machinery: one thread waits on a barrier that nothing ever arrives on, with a
+// limit of `limit_us` microseconds; the wait gives up, records kErrWaitConsumer in the status word and the kernel
+// returns normally (no trap, no unbounded loop).  A second wait in the same CTA returns at once (abort flag).
+__global__ void wait_timeout_selftest_kernel(int* status, unsigned long long limit_ns, int* observed) {
+  __shared__ uint64_t bar;
+  __shared__ CtaCtl ctl;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    ctl.abort = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool first = mbar_wait_limit(&bar, 0, &ctl, status, kErrWaitConsumer, limit_ns);
+    const unsigned long long t0 = global_timer_ns();
+    const bool second = mbar_wait_limit(&bar, 0, &ctl, status, kErrWaitTma, limit_ns);
+    const unsigned long long dt = global_timer_ns() - t0;
+    if (observed != nullptr) {
+      observed[0] = first ? 1 : 0;
+      observed[1] = second ? 1 : 0;
+      observed[2] = dt < limit_ns ? 1 : 0;       // the second wait did not sit out the limit again
+    }
+  }
+}
+
+int launch_wait_timeout_selftest(int* status, int limit_us, int* observed, cudaStream_t st) {
+  if (status == nullptr || limit_us <= 0 || limit_us > 100000) return -1;
+  wait_timeout_selftest_kernel<<<1, 32, 0, st>>>(status, static_cast<unsigned long long>(limit_us) * 1000ull, observed);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace fm

@@ -234,7 +234,9 @@ def band_attention_prefill(q, k, v, *, window=250, scale=0.125, out=None, status
 
 def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtype=torch.float16,
                       workspace=None, out=None, status=None):
-    """Projection + RoPE + banded attention for a call without cache; returns ``[B,T,512]`` value_dtype."""
+    """Projection + RoPE + banded attention for a call without cache; returns ``[B,T,512]`` value_dtype: the
+    projection kernel followed by the attention kernel that fits the clip length (``attention_fused`` does the same
+    in one kernel for clips of 129 .. 256 frames, without the q / k / v workspace)."""
     lib = _native.load()
     _need(x.dim() == 3, "x must be [B, T, 512]")
     B, T, _ = x.shape
@@ -538,6 +540,50 @@ def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates
                                    _stream())
         _native.check(rc, "fm_rvq_select_f32")
     return (codes, cand) if return_candidates else codes
+
+
+def split_half(x):
+    """``x`` (float32, contiguous, a multiple of 8 values) as ``hi + lo`` with both parts float16."""
+    lib = _native.load()
+    _need(x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.numel() % 8 == 0,
+          "x must be a contiguous CUDA float32 tensor with a multiple of 8 values")
+    hi = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    lo = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    _native.check(lib.fm_split_half(x.data_ptr(), hi.data_ptr(), lo.data_ptr(), x.numel(), _stream()), "fm_split_half")
+    return hi, lo
+
+
+def linear_split(x, w_parts, *, status=None):
+    """``x [rows, K] @ w^T`` with FP32-grade accuracy on the FP16 tensor core: ``x`` float32, ``w_parts`` the pair
+    ``split_half(w)`` of a float32 ``[N, K]`` weight.  Three products with FP32 accumulation chained through the
+    linear kernel's FP32 residual input: ``hi W_hi + hi W_lo + lo W_hi`` (the dropped ``lo W_lo`` term is below
+    2^-22 of the result).  K a multiple of 64, N of 256."""
+    w_hi, w_lo = w_parts
+    x_hi, x_lo = split_half(x.contiguous())
+    y = linear(x_hi, w_lo, out_dtype=torch.float32, status=status)
+    y2 = linear(x_lo, w_hi, residual=y, out_dtype=torch.float32, status=status)
+    return linear(x_hi, w_hi, residual=y2, out_dtype=torch.float32, out=y, status=status)
+
+
+def downsample_conv(x, w_parts, *, kernel=4, stride=2, status=None):
+    """The stride-2 causal, replicate-padded, bias-free convolution after the encoder transformer on frame-major
+    activations: ``x [B, T, C]`` float32 -> ``[B, ceil(T / stride), C_out]`` float32.  ``w_parts`` =
+    ``split_half(weight.permute(0, 2, 1).reshape(C_out, kernel * C))`` for an ``nn.Conv1d`` weight
+    ``[C_out, C, kernel]``.  FP32-grade accuracy (split-precision tensor-core products)."""
+    lib = _native.load()
+    _need(x.is_cuda and x.dtype == torch.float32 and x.dim() == 3 and x.is_contiguous(), "x must be contiguous CUDA float32 [B, T, C]")
+    B, T, C = x.shape
+    w_hi, w_lo = w_parts
+    _need(w_hi.shape == w_lo.shape and w_hi.shape[1] == kernel * C, f"weight parts must be [C_out, {kernel * C}]")
+    t_out = (T + stride - 1) // stride
+    hi = torch.empty(B * t_out, kernel * C, dtype=torch.float16, device=x.device)
+    lo = torch.empty_like(hi)
+    _native.check(lib.fm_conv_rows_split(x.data_ptr(), hi.data_ptr(), lo.data_ptr(), B, T, C, kernel, stride, _stream()),
+                  "fm_conv_rows_split")
+    y = linear(hi, w_lo, out_dtype=torch.float32, status=status)
+    y2 = linear(lo, w_hi, residual=y, out_dtype=torch.float32, status=status)
+    y = linear(hi, w_hi, residual=y2, out_dtype=torch.float32, out=y, status=status)
+    return y.view(B, t_out, w_hi.shape[0])
 
 
 def rvq_decode(codes, books: RVQCodebooks):

@@ -3,8 +3,9 @@
 ``MimiRVQB200`` mirrors ``MimiResidualVectorQuantizer`` (src/fast_mimi/model.py:2365-2444): ``encode(embeddings
 [B, hidden, T], num_quantizers) -> int64 [K, B, T]`` and ``decode(codes [B, K, T]) -> float32 [B, hidden, T]``;
 ``MimiSplitRVQB200`` mirrors ``MimiSplitResidualVectorQuantizer`` (src/fast_mimi/model.py:2447-2480): one semantic
-stack plus one acoustic stack on the same embeddings.  The 1 x 1 convolutions ``input_proj`` / ``output_proj`` run as
-FP32 linears, the codebook search on ``ops.rvq_encode`` (tensor-core pre-selection, exact FP32 decision) and the
+stack plus one acoustic stack on the same embeddings.  The 1 x 1 convolutions ``input_proj`` / ``output_proj`` run on
+the tensor core as split-precision products (``ops.linear_split``: FP16 hi + lo parts, FP32 accumulation, the accuracy
+of an FP32 linear, which the code decisions downstream need), the codebook search on ``ops.rvq_encode`` (tensor-core pre-selection, exact FP32 decision) and the
 ordered sum on ``ops.rvq_decode``.  Codebook vectors are taken from the reference modules
 (``layer.codebook.embed``) when the wrapper is built; rebuild it after loading new weights.
 """
@@ -19,8 +20,19 @@ from . import ops
 class MimiRVQB200:
     def __init__(self, codebooks: torch.Tensor, input_proj: torch.Tensor | None, output_proj: torch.Tensor | None) -> None:
         self.books = ops.RVQCodebooks(codebooks)
-        self.input_proj = None if input_proj is None else input_proj.detach().float().reshape(input_proj.shape[0], -1).contiguous()
-        self.output_proj = None if output_proj is None else output_proj.detach().float().reshape(output_proj.shape[0], -1).contiguous()
+        flat = lambda w: None if w is None else w.detach().float().reshape(w.shape[0], -1).contiguous()
+        self.input_proj, self.output_proj = flat(input_proj), flat(output_proj)
+        # FP16 hi + lo parts of the projection weights for the tensor-core products
+        self._in_parts = None if self.input_proj is None else ops.split_half(self.input_proj)
+        self._out_parts = None if self.output_proj is None else ops.split_half(self.output_proj)
+
+    @staticmethod
+    def _project(x: torch.Tensor, w: torch.Tensor, parts) -> torch.Tensor:
+        # the tensor-core kernel takes K in multiples of 64 and N in multiples of 256 (Mimi: 512 -> 256 and back);
+        # other geometries (the reference's tiny test configuration) take the FP32 CUDA-core kernel
+        if w.shape[1] % 64 == 0 and w.shape[0] % 256 == 0:
+            return ops.linear_split(x, parts)
+        return ops.linear_fp32(x, w)
 
     @classmethod
     def from_reference(cls, rvq: nn.Module) -> "MimiRVQB200":
@@ -35,7 +47,7 @@ class MimiRVQB200:
         B, _, T = embeddings.shape
         x = embeddings.float().permute(0, 2, 1).reshape(B * T, -1)
         if self.input_proj is not None:
-            x = ops.linear_fp32(x.contiguous(), self.input_proj)
+            x = self._project(x.contiguous(), self.input_proj, self._in_parts)
         codes = ops.rvq_encode(x.contiguous(), self.books, num_quantizers)
         # codes are the end of the device pipeline: a recorded error (a timed-out wait in a kernel upstream, a
         # non-finite residual) must not leave as plausible-looking indices
@@ -47,7 +59,7 @@ class MimiRVQB200:
         B, K, T = codes.shape
         q = ops.rvq_decode(codes.transpose(0, 1).reshape(K, B * T).contiguous(), self.books)
         if self.output_proj is not None:
-            q = ops.linear_fp32(q, self.output_proj)
+            q = self._project(q, self.output_proj, self._out_parts)
         return q.view(B, T, -1).permute(0, 2, 1).contiguous()
 
 

@@ -28,6 +28,14 @@ extern "C" {
 
 int fm_abi_version(void);
 
+/* Self-test of the bounded device waits every kernel of this library uses (no counterpart in the reference, whose
+ * kernels do not wait on one another): a one-thread kernel waits, with a limit of limit_us microseconds (at most
+ * 100 000), on a barrier that nothing arrives on.  The wait gives up, code 103 lands in *status and the kernel
+ * returns normally.  observed (3 ints, may be NULL): whether the first wait succeeded (0 expected), whether a second
+ * wait in the same block succeeded (0), whether that second wait returned at once because the block was already
+ * marked aborted (1). */
+int fm_selftest_wait_timeout(int* status, int limit_us, int* observed, void* stream);
+
 /* q|k|v = x W_qkv^T with rotate-half RoPE applied to q and k in the FP32 epilogue.
  * Replaces q_proj/k_proj/v_proj + _apply_rope (src/fast_mimi/model.py:1897-1912; packed-weight form
  * src/fast_mimi/_packed_qkv.py:139-171).
@@ -50,8 +58,10 @@ int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void*
 /* The same computation as fm_attention_prefill_bf16 in ONE kernel for clips of 128 < T <= 256 frames (Mimi's
  * 10 s clips): x and W_qkv in, attention output out, the rotated q, k, v never reach memory, so no workspace.
  * Replaces src/fast_mimi/model.py:1897-1914 + :1627-1688 + :1860-1868 for such clips (the reference's own fused
- * front half: src/fast_mimi/_packed_qkv.py:14-131,152-202).  Other T: returns -6 (use fm_attention_prefill_bf16,
- * which routes here by itself when T fits).  value_dtype as for fm_qkv_rope_bf16. */
+ * front half: src/fast_mimi/_packed_qkv.py:14-131,152-202).  Other T: returns -6 (use fm_attention_prefill_bf16).
+ * It moves 2.5 times fewer bytes through HBM than the two-kernel entry point; on B200 it is currently the slower of
+ * the two in time, which is why fm_attention_prefill_bf16 does not route to it.  value_dtype as for
+ * fm_qkv_rope_bf16. */
 int fm_attention_fused_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                             void* out, int B, int T, int window, float scale, int value_dtype, int* status,
                             void* stream);
@@ -117,6 +127,21 @@ int fm_layernorm_f16(const void* x, int x_dtype, const float* weight, const floa
 int fm_rvq_select_f32(const void* scores, int scores_dtype, const float* e_sq, const float* codebook,
                       float* residual, void* residual16, long long* codes, int* n_candidates, long long rows,
                       int n_codes, float e_max, float tau_rel, int* status, void* stream);
+
+/* Input rows of the stride-2 downsampling convolution that follows the encoder transformer (MimiModel.downsample:
+ * MimiConv1d(512, 512, kernel 4, stride 2, no bias, replicate padding, causal), src/fast_mimi/model.py:2734-2744):
+ * for frame-major FP32 x [B, T, C], row (b, t) of the result is frames stride*t - (kernel - stride) .. + kernel - 1
+ * of clip b, clamped to the clip (replicate padding on both sides), C values each, as FP16 hi + lo parts
+ * [B * ceil(T / stride), kernel * C].  The convolution itself is then fm_linear_f16 with the kernel laid out as
+ * [C_out, kernel * C_in] (three products: hi W_hi + hi W_lo + lo W_hi, FP32 residual chaining). */
+int fm_conv_rows_split(const float* x, void* hi, void* lo, int B, int T, int C, int kernel, int stride, void* stream);
+
+/* x = hi + lo, both FP16 (hi = round(x), lo = round(x - hi)), n a multiple of 8 values: the operands of an
+ * FP32-grade product on the FP16 tensor core (hi W_hi + hi W_lo + lo W_hi via fm_linear_f16 with FP32 residual
+ * chaining).  Used for the quantiser's 1 x 1 input / output projections (nn.Conv1d(kernel 1, no bias),
+ * src/fast_mimi/model.py:2392-2406, applied at :2417 and :2443), whose results decide code indices and must
+ * therefore keep FP32 accuracy. */
+int fm_split_half(const float* x, void* hi, void* lo, long long n, void* stream);
 
 /* FP16 copy of [rows, 256] FP32 values (the residual before the first layer). */
 int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream);

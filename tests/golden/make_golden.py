@@ -252,6 +252,27 @@ def end_to_end_codes(seconds: int = 5):
     print("codes", tuple(codes.shape), "distinct", len(torch.unique(codes)))
 
 
+def downsample():
+    """The reference's stride-2 ``downsample`` convolution (MimiModel.downsample, model.py:2734-2744) on seeded
+    transformer-output-like frames of odd and even lengths; outputs at a few frames."""
+    from fast_mimi.model import MimiConv1d
+    cfg = MimiConfig()
+    torch.manual_seed(51)
+    conv = MimiConv1d(cfg, cfg.hidden_size, cfg.hidden_size, 4, stride=2, bias=False, pad_mode="replicate").eval()
+    with torch.no_grad():
+        conv.conv.weight.copy_(torch.randn(conv.conv.weight.shape) / (4 * cfg.hidden_size) ** 0.5)
+    arrays = dict(seed=51, weight_probe=conv.conv.weight[:2, :3])
+    for t in (125, 250, 7):
+        x = torch.randn(2, t, cfg.hidden_size)
+        with torch.inference_mode():
+            y = conv(x.transpose(1, 2)).transpose(1, 2)               # [2, ceil(t/2), 512]
+        rows = np.array(sorted(set([0, 1, 2, y.shape[1] // 2, y.shape[1] - 2, y.shape[1] - 1])))
+        arrays[f"rows{t}"] = rows
+        arrays[f"out{t}"] = y[:, rows]
+        arrays[f"frames{t}"] = y.shape[1]
+    save("downsample.npz", **arrays)
+
+
 def rvq_codes():
     """Residual quantiser stack of the reference (7 layers, 2048 x 256 codebooks, 1x1 input projection) on seeded
     embeddings [2, 512, 40]: codes, and the decoded sum before the output projection at a few frames."""
@@ -298,3 +319,4 @@ if __name__ == "__main__":
     for seconds in (5, 10, 12):
         end_to_end_codes(seconds)
     rvq_codes()
+    downsample()

@@ -44,9 +44,53 @@ def test_rvq_codes_match_the_oracle(rows, layers, scores_dtype):
     want = O.rvq_encode(x, books)
     gb = fm.ops.RVQCodebooks(books.cuda())
     got = fm.ops.rvq_encode(x.cuda(), gb, scores_dtype=scores_dtype).cpu()
-    same = (got == want).all(dim=0).float().mean()
-    assert same >= 0.995, float(same)
+    frames_same = int((got == want).all(dim=0).sum())
+    # Where a frame differs, the two nearest entries are closer together than FP32 rounding resolves: the oracle
+    # (like the reference) takes argmin over torch.cdist, which for more than 25 rows evaluates |x|^2 + |e|^2 - 2 x.e
+    # through a matrix product, the kernel decides by sum_k (x_k - e_k)^2.  An FP64 evaluation of the exact
+    # distances says which of the two is nearer to the truth at the first layer where they part.
+    first_diff = (got != want).int().argmax(dim=0)
+    differing = ((got != want).any(dim=0)).nonzero().flatten().tolist()
+    ours_better = 0
+    for r in differing:
+        l = int(first_diff[r])
+        resid = x[r].double()
+        for j in range(l):
+            resid = resid - books[j, got[j, r]].double()
+        d = ((resid[None] - books[l].double()) ** 2).sum(-1)
+        ours_better += int(d[got[l, r]] <= d[want[l, r]])
+    print(f"rvq rows={rows} layers={layers} scores={scores_dtype}: {frames_same} of {rows} frames have all codes equal to "
+          f"the oracle's; of the {len(differing)} others the kernel's choice is the nearer one in FP64 for {ours_better}")
+    assert frames_same >= 0.995 * rows, frames_same
     assert torch.equal(fm.ops.rvq_decode(got.cuda(), gb).cpu(), O.rvq_decode(got, books))
+
+
+@pytest.mark.parametrize("rows,n,k", [(1000, 256, 512), (64, 512, 256), (4099, 256, 512)])
+def test_split_precision_linear_has_fp32_accuracy(rows, n, k):
+    """The quantiser's input / output projections on the FP16 tensor core (hi + lo parts, FP32 accumulation) against
+    an FP64 product and against the FP32 verification kernel."""
+    import fast_mimi_b200 as fm
+    g = torch.Generator().manual_seed(rows)
+    x = (torch.randn(rows, k, generator=g) * 3).cuda()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).cuda()
+    got = fm.ops.linear_split(x, fm.ops.split_half(w))
+    ref64 = (x.double() @ w.double().T)
+    err = float((got.double() - ref64).abs().max() / ref64.abs().max())
+    err32 = float((fm.ops.linear_fp32(x, w).double() - ref64).abs().max() / ref64.abs().max())
+    print(f"split-precision linear {rows}x{k}->{n}: max error / max |y| = {err:.2e} (FP32 CUDA-core kernel: {err32:.2e})")
+    assert err < 1e-6
+
+
+def test_non_finite_residual_is_reported_not_quantised():
+    import fast_mimi_b200 as fm
+    gb = fm.ops.RVQCodebooks(torch.randn(1, 256, 256).cuda())
+    x = torch.randn(4, 256).cuda()
+    x[2, 7] = float("nan")
+    st = fm.ops.new_status("cuda")
+    fm.ops.rvq_encode(x, gb, status=st)
+    assert fm.ops.read_status(st) == 105
+    with pytest.raises(RuntimeError, match="105"):
+        fm.check_status(status=st)
 
 
 def test_rvq_decode_rejects_out_of_range_codes():
@@ -90,7 +134,9 @@ def test_split_quantizer_wrapper_matches_oracle_encode_and_decode():
     want = torch.cat((oracle_encode(sem, sem_books, 1), oracle_encode(aco, aco_books, 7)))
     got = native.encode(emb.cuda(), 8).cpu()
     assert got.shape == (8, 3, 50)
-    assert (got == want).all(dim=0).float().mean() >= 0.995
+    same = int((got == want).all(dim=0).sum())
+    print(f"split quantiser wrapper: {same} of 150 frames have all 8 codes equal to the oracle's")
+    assert same >= 0.995 * 150
     assert torch.equal(native.encode(emb.cuda(), 3).cpu(), got[:3])
 
     codes = got.permute(1, 0, 2).contiguous()                       # [B, K, T] as the reference's decode takes them

@@ -380,6 +380,80 @@ def test_preset_status_word_makes_kernels_return_untouched_outputs():
     assert not bool(torch.isnan(out.float()).any())
 
 
+def test_bounded_wait_gives_up_and_reports():
+    """The bounded-wait machinery itself: a barrier that nothing arms, a 2 ms limit; the kernel ends by itself with
+    code 103 in the status word, and a later wait in the same block returns at once."""
+    import fast_mimi_b200 as fm
+    lib = fm._native.load()
+    st = fm.ops.new_status("cuda")
+    seen = torch.full((3,), -1, dtype=torch.int32, device="cuda")
+    rc = lib.fm_selftest_wait_timeout(st.data_ptr(), 2000, seen.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert fm.ops.read_status(st) == 103
+    assert seen.tolist() == [0, 0, 1]
+    with pytest.raises(RuntimeError, match="103"):
+        fm.check_status(status=st)
+
+
+@pytest.mark.parametrize("T", [129, 200, 256])
+@pytest.mark.parametrize("window", [1, 8, 100, 129, 200, 256])
+def test_whole_clip_kernels_with_other_windows(T, window):
+    """Clips of 129..256 frames under windows that leave rows of the second tile with nothing visible in the first
+    (window <= 128) and windows that cut into it: the clip-attention kernel (q, k, v given) and the fused kernel
+    (x given) against the oracle."""
+    import fast_mimi_b200 as fm
+    torch.manual_seed(T * 1000 + window)
+    x = torch.randn(2, T, 512).bfloat16()
+    w = (torch.randn(1536, 512) * 0.03).bfloat16()
+    cos, sin = O.rope_tables(torch.arange(T))
+    q, k, v = O.qkv_project(x.float(), *w.float().chunk(3, 0))
+    q, k = O.apply_rope(q, k, cos, sin)
+    want = O.band_attention(q, k, v, window=window).transpose(1, 2).reshape(2, T, 512)
+    dev = lambda t: t.cuda()
+    fused = fm.ops.attention_fused(dev(x), dev(w), dev(cos[None]), dev(sin[None]), window=window)
+    assert O.rel_l2(fused.float().cpu(), want) < TOL
+    qd, kd, vd = fm.ops.qkv_rope(dev(x), dev(w), dev(cos[None]), dev(sin[None]))
+    clip = fm.ops.band_attention_prefill(qd, kd, vd, window=window)
+    assert O.rel_l2(clip.float().cpu(), want) < TOL
+    fm.check_status()
+
+
+def test_decode_with_a_different_position_per_stream_across_the_wrap():
+    """16 streams at positions (37 s) % 600 + step, stepped over the ring's wrap (249 -> 250 -> 251 for some of
+    them), per-stream tables [S, 1, 64] and a device-side stream_pos: every stream's step against the last row of a
+    cache-free prefill over that stream's own history."""
+    import fast_mimi_b200 as fm
+    torch.manual_seed(5)
+    S, steps = 16, 4
+    w = (torch.randn(1536, 512) * 0.03).bfloat16()
+    base = (torch.arange(S) * 37) % 600
+    hist = [torch.randn(int(base[s]) + steps, 512).bfloat16() for s in range(S)]     # frames 0 .. base+steps-1 of stream s
+    ring = fm.MimiKVRing(1, S, 250, device="cuda")
+    # seed every ring with its stream's first `base` frames through the chunk path (per stream: lengths differ)
+    for s in range(S):
+        n = int(base[s])
+        if n == 0:
+            continue
+        cos, sin = O.rope_tables(torch.arange(n))
+        one = fm.MimiKVRing(1, 1, 250, device="cuda")
+        fm.ops.attention_chunk(hist[s][None, :n].cuda(), w.cuda(), cos[None].cuda(), sin[None].cuda(), one.ring_k[0], one.ring_v[0], 0)
+        ring.ring_k[0, s].copy_(one.ring_k[0, 0]); ring.ring_v[0, s].copy_(one.ring_v[0, 0])
+    pos = base.to(torch.int32).cuda()
+    for t in range(steps):
+        xs = torch.stack([hist[s][int(base[s]) + t] for s in range(S)])
+        cs = [O.rope_tables(torch.tensor([int(base[s]) + t])) for s in range(S)]
+        cos = torch.stack([c[0] for c in cs]).cuda(); sin = torch.stack([c[1] for c in cs]).cuda()      # [S, 1, 64]
+        got = fm.ops.decode_step(xs.cuda(), w.cuda(), cos, sin, ring.ring_k[0], ring.ring_v[0], t, stream_pos=pos).cpu()
+        for s in range(S):
+            n = int(base[s]) + t + 1
+            c_, s_ = O.rope_tables(torch.arange(n))
+            q, k, v = O.qkv_project(hist[s][None, :n].float(), *w.float().chunk(3, 0))
+            q, k = O.apply_rope(q, k, c_, s_)
+            want = O.band_attention(q[:, :, -1:], k, v, q_offset=n - 1).transpose(1, 2).reshape(512)
+            assert O.rel_l2(got[s], want) < TOL, (s, t, n)
+    fm.check_status()
+
+
 def test_module_rejects_what_it_does_not_implement():
     import fast_mimi_b200 as fm
     m = fm.MimiAttentionB200().cuda()

@@ -91,6 +91,20 @@ def test_mimi_size_cached_chunks_match_reference():
     assert (cache.values[0][:, :, -3:] - g["final_value_cache"]).abs().max() < TOL
 
 
+def test_downsample_conv_matches_reference():
+    """The oracle's stride-2 convolution against the reference's MimiConv1d (causal, replicate padding, no bias)."""
+    g = load_golden("downsample.npz")
+    torch.manual_seed(int(g["seed"]))
+    torch.nn.Conv1d(512, 512, 4, 2, bias=False)             # the reference module's own initialisation draws first
+    weight = torch.randn(512, 512, 4) / (4 * 512) ** 0.5
+    assert torch.equal(weight[:2, :3], g["weight_probe"])
+    for t in (125, 250, 7):
+        x = torch.randn(2, t, 512)
+        y = O.downsample_conv(x, weight)
+        assert y.shape[1] == int(g[f"frames{t}"]) == (t + 1) // 2
+        assert (y[:, g[f"rows{t}"]] - g[f"out{t}"]).abs().max() < TOL
+
+
 def test_ring_decode_260_matches_reference():
     g = load_golden("ring_decode_260.npz")
     wq, wk, wv, wo = regen_projections(int(g["seed"]))

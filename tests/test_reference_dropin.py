@@ -72,7 +72,7 @@ def _reference_model(device):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("seconds", [5, 10, 12])
-@pytest.mark.parametrize("swap", ["attention", "layers"])
+@pytest.mark.parametrize("swap", ["attention", "layers", "layers+downsample+rvq"])
 def test_codes_through_the_reference_model_match_its_cpu_result(swap, seconds):
     """benchmark config 1 inside the reference's MimiModel: encode() hands the installed modules its own mask and
     rotary tables; code frames vs the reference's CPU codes (tests/golden/e2e_codes_*s.npz) >= 99.5 %."""
@@ -83,6 +83,9 @@ def test_codes_through_the_reference_model_match_its_cpu_result(swap, seconds):
     with torch.inference_mode():
         stock = model.encode(audio, num_quantizers=8).audio_codes.cpu()
         (fm.install if swap == "attention" else fm.install_layers)(model.encoder_transformer)
+        if swap == "layers+downsample+rvq":      # encoder transformer -> downsample -> quantiser: one native chain
+            model.downsample = fm.MimiDownsampleB200(model.downsample)
+            model.quantizer.encode = fm.MimiSplitRVQB200.from_reference(model.quantizer).encode
         ours = model.encode(audio, num_quantizers=8).audio_codes.cpu()
     fm.check_status()
     golden = g["codes"]
