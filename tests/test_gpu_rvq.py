@@ -78,7 +78,7 @@ def test_split_precision_linear_has_fp32_accuracy(rows, n, k):
     err = float((got.double() - ref64).abs().max() / ref64.abs().max())
     err32 = float((fm.ops.linear_fp32(x, w).double() - ref64).abs().max() / ref64.abs().max())
     print(f"split-precision linear {rows}x{k}->{n}: max error / max |y| = {err:.2e} (FP32 CUDA-core kernel: {err32:.2e})")
-    assert err < 1e-6
+    assert err < 2e-6 and err < 2 * err32 + 1e-7       # as good as an FP32 product of the same operands
 
 
 def test_non_finite_residual_is_reported_not_quantised():
