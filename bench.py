@@ -12,12 +12,18 @@ Clips are independent, so ranks share nothing on the data path (weak scaling: 51
 One JSON line is printed by rank 0.  `value` is device-resident throughput; `e2e` includes the
 host->device copy of the batch from pinned memory and the device->host copy of the last layer's output
 every step.  `roofline` describes the kernel with the largest share of the step, timed with CUDA events
-on the launching stream inside the timed region.  `cpu_baseline` is the CPU oracle (a PyTorch FP32
-restatement of the reference's attention, all host threads) on a bounded sample of the same workload.
-`decode` adds the streaming single-frame step (benchmark config 5) on a full 250-slot ring.
+on the launching stream inside the timed region; `kernels` lists both kernels of the step and, timed after
+it, the fused one-kernel form of the same layer call.  `parity` compares the timed configuration's own
+output (full-size launches, 8 clips x 16 layers) with the CPU oracle.  `strong` is the same workload with
+the 512 clips split over the GPUs (benchmark config 3 as stated), `longclip` benchmark config 4 with its 16
+clips split over the GPUs, `host_copy` the pinned-memory copies of the e2e loop without kernels (the
+ceiling the host side puts on `e2e`), `decode` the streaming single-frame step (benchmark config 5) on a
+full 250-slot ring.  `cpu_baseline` is the CPU arm on a fixed 64-clip sample of the same workload.
 
-`--impl reference` times that CPU restatement instead (the reference is PyTorch code whose CPU path is
-exactly these library calls; the reference checkout itself does not travel to the GPU box).
+`--impl reference` times the CPU arm alone: the reference's own MimiAttention.forward (FP32, all host
+threads) where its package has been placed under oracle/_ref by oracle/make_ref.py, else the oracle's
+restatement of the same calls; the line's cpu_baseline.kind says which.
+`--workload longclip | stream | streamlayer | stack | rvq` print one line each for the secondary workloads.
 """
 from __future__ import annotations
 
@@ -763,14 +769,14 @@ def run_extra_workload(args) -> None:
         ms = a.elapsed_time(b) / args.steps
         ms_proj = b.elapsed_time(c) / args.steps
         flop = rows * layers * 2 * 2048 * 256
-        nbytes = rows * layers * (2 * 2048 * 2 + 256 * (2 + 4 + 4 + 2))     # FP16 scores written + read, residual in both types
+        nbytes = rows * layers * (2 * 32 * 16 + 256 * (2 + 4 + 4 + 2))      # candidate records written + read, residual in both types
         print(json.dumps({"metric": "quantised vectors/s", "value": rows / (ms / 1e3), "unit": "vectors/s", "n_gpus": 1,
                           "steps": args.steps, "ms_per_step": ms, "dtype": "fp16 pre-selection, fp32 decision", "data": "synthetic",
                           "config": {"workload": "residual vector quantisation encode, 8 codebooks x 2048 x 256",
                                      "vectors": rows, "layers": layers},
                           "tensor_tflops": flop / (ms / 1e3) / 1e12, "gbs": nbytes / (ms / 1e3) / 1e9,
                           "frac_hbm": nbytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"],
-                          "input_projection_ms": ms_proj,
+                          "input_projection_ms": ms_proj, "scores_in_memory": False,
                           "exact_evaluations_per_vector_layer": float(cand.float().mean())}))
         return
     if args.workload == "longclip":

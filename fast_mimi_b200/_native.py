@@ -23,11 +23,16 @@ SIGNATURES: dict[str, list] = {
     "fm_layernorm_f16": [_P, _I, _P, _P, _F, _P, _I, _LL, _P],
     "fm_rvq_select_f32": [_P, _I, _P, _P, _P, _P, _P, _P, _LL, _I, _F, _F, _P, _P],
     "fm_conv_rows_split": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "fm_upsample2_f32": [_P, _P, _P, _I, _I, _I, _P],
     "fm_split_half": [_P, _P, _P, _LL, _P],
+    "fm_rvq_prepare_f32": [_P, _P, _P, _LL, _F, _F, _P],
+    "fm_rvq_candidates_f16": [_P, _P, _P, _P, _P, _LL, _I, _P, _P],
+    "fm_rvq_select_rec_f32": [_P, _P, _P, _P, _P, _P, _P, _LL, _I, _F, _F, _P, _P],
     "fm_rvq_to_half": [_P, _P, _LL, _P],
     "fm_rvq_decode_f32": [_P, _P, _P, _LL, _I, _I, _P, _P],
     "fm_band_attn_prefill_bf16": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_prefill_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
+    "fm_band_attn_chunk_bf16": [_P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_fused_bf16": [_P, _P, _P, _P, _LL, _P, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_chunk_bf16": [_P, _P, _P, _P, _LL, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "fm_attention_prefill_static_bf16": [_P, _P, _P, _P, _LL, _P, _I, _I, _I, _F, _I, _P, _P],

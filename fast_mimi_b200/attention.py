@@ -203,7 +203,7 @@ class MimiAttentionB200(nn.Module):
             return ops.attention_prefill(x, w, cos, sin, window=self.sliding_window, scale=self.scaling,
                                          value_dtype=self.value_dtype)
         if not isinstance(cache, MimiKVRing):
-            raise RuntimeError("the tensor-core path needs a MimiKVRing cache (see new_cache)")
+            return self._forward_tc_foreign_cache(x, w, cos, sin, cache)
         ops._need(cache.num_streams == B, "cache was created for a different number of streams")
         ops._need(cache.sliding_window == self.sliding_window, "cache window differs from the module's")
         pos = cache.get_seq_length(self.layer_idx)
@@ -216,6 +216,24 @@ class MimiAttentionB200(nn.Module):
                                       scale=self.scaling)
         cache.advance(self.layer_idx, T)
         return out.view(B, T, 512)
+
+    def _forward_tc_foreign_cache(self, x, w, cos, sin, cache):
+        """A cache object that is not a ``MimiKVRing`` but speaks the reference's ``MimiKVCache`` protocol
+        (``get_seq_length``, ``update`` returning the visible K / V: src/fast_mimi/model.py:435-471), e.g. the cache
+        ``MimiTransformerModel.forward`` creates by itself under ``use_cache=True``.  Projection and attention run on
+        the tensor-core kernels; the cache keeps its own storage (its rotated K / V are the kernels' 16-bit values,
+        so nothing is rounded twice) and the visible rows are laid out frame-major for the attention kernel by
+        PyTorch copies.  Slower than the ring (the reference's concatenate-and-crop stays), same results."""
+        if not (hasattr(cache, "update") and hasattr(cache, "get_seq_length")):
+            raise RuntimeError("past_key_values must be a MimiKVRing or offer MimiKVCache's update / get_seq_length")
+        B, T, _ = x.shape
+        q, k, v = ops.qkv_rope(x, w, cos, sin, value_dtype=self.value_dtype)
+        heads = lambda t: t.view(B, T, self.num_heads, self.head_dim).transpose(1, 2)
+        k_all, v_all = cache.update(heads(k).float(), heads(v).float(), self.layer_idx)     # [B, 8, Tk, 64]
+        Tk = k_all.shape[2]
+        frames = lambda t, dt: t.transpose(1, 2).reshape(B, Tk, self.num_heads * self.head_dim).to(dt).contiguous()
+        return ops.band_attention_chunk(q, frames(k_all, torch.bfloat16), frames(v_all, self.value_dtype),
+                                        window=self.sliding_window, scale=self.scaling)
 
     def _forward_fp32(self, hidden_states, cache, cos, sin):
         B, T, _ = hidden_states.shape

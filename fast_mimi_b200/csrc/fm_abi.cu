@@ -109,6 +109,13 @@ int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos
                              status, stream);
 }
 
+int fm_band_attn_chunk_bf16(const void* q, const void* k, const void* v, void* out, int B, int Tq, int Tk, int window,
+                            float scale, int value_dtype, int* status, void* stream) {
+  if (value_dtype != 0 && value_dtype != 1) return -1;
+  return fm::launch_band_attn_chunk(q, k, v, out, B, Tq, Tk, window, scale, value_dtype, status,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int fm_attention_fused_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                             void* out, int B, int T, int window, float scale, int value_dtype, int* status,
                             void* stream) {
@@ -173,8 +180,31 @@ int fm_conv_rows_split(const float* x, void* hi, void* lo, int B, int T, int C, 
   return fm::launch_conv_rows_split(x, hi, lo, B, T, C, kernel, stride, static_cast<cudaStream_t>(stream));
 }
 
+int fm_upsample2_f32(const float* x, const float* w, float* y, int B, int T, int C, void* stream) {
+  return fm::launch_upsample2_depthwise(x, w, y, B, T, C, static_cast<cudaStream_t>(stream));
+}
+
 int fm_split_half(const float* x, void* hi, void* lo, long long n, void* stream) {
   return fm::launch_split_half(x, hi, lo, n, static_cast<cudaStream_t>(stream));
+}
+
+int fm_rvq_candidates_f16(const void* residual16, const void* codebook16, const float* e_sq, const float* tau,
+                          void* records, long long rows, int n_codes, int* status, void* stream) {
+  if (rows < 0 || rows > 0x7fffffffLL) return -1;
+  return fm::launch_linear_gemm(residual16, codebook16, records, e_sq, tau, static_cast<int>(rows), n_codes, 256, 1, 3, 0,
+                                status, static_cast<cudaStream_t>(stream));
+}
+
+int fm_rvq_select_rec_f32(const void* records, const float* codebook, float* residual, void* residual16, long long* codes,
+                          int* n_candidates, float* tau, long long rows, int n_codes, float e_max_next, float tau_rel,
+                          int* status, void* stream) {
+  return fm::launch_rvq_select_rec(records, codebook, residual, residual16, codes, n_candidates, tau, rows, n_codes,
+                                   e_max_next, tau_rel, status, static_cast<cudaStream_t>(stream));
+}
+
+int fm_rvq_prepare_f32(const float* x, void* residual16, float* tau, long long rows, float e_max, float tau_rel,
+                       void* stream) {
+  return fm::launch_rvq_prepare(x, residual16, tau, rows, e_max, tau_rel, static_cast<cudaStream_t>(stream));
 }
 
 int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream) {

@@ -442,6 +442,17 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Per-warpgroup register budget (four consecutive warps, aligned; one instruction executed by all of them).  A
+// kernel whose launch bound leaves every thread R registers may hand registers of warps that need few to warps that
+// need many: the donors shrink first, the receivers' request blocks until the registers are free, so the sum after
+// all requests must not exceed threads x R.
+template <int N> __device__ __forceinline__ void warpgroup_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void warpgroup_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // 16-bit storage types of the value path.
 template <typename T> struct Pack16;
 template <> struct Pack16<__half> {

@@ -1,5 +1,7 @@
-// Stride-2 downsampling convolution between the encoder transformer and the quantiser (sm_100a).
+// The two stride-2 convolutions around the quantiser (sm_100a): `downsample` after the encoder transformer and
+// `upsample` before the decoder transformer.
 //
+// Downsample.
 // Reference: MimiModel.downsample = MimiConv1d(512 -> 512, kernel 4, stride 2, no bias, replicate padding, causal)
 // (src/fast_mimi/model.py:2734-2744; forward of the class: left padding kernel - stride = 2 frames, right padding
 // (-T) % 2 frames, both repeating the edge frame, then nn.Conv1d).  On frame-major activations [B, T, 512] output
@@ -57,6 +59,50 @@ int launch_conv_rows_split(const float* x, void* hi, void* lo, int B, int T, int
   const long long want = (total + 255) / 256, cap = static_cast<long long>(sms > 0 ? sms : 1) * 8;
   conv_rows_split_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, st>>>(
       x, static_cast<uint16_t*>(hi), static_cast<uint16_t*>(lo), B, T, T_out, C, kernel, stride);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Upsample.  Reference: MimiModel.upsample = MimiConvTranspose1d(512 -> 512, kernel 4, stride 2, groups = 512, no bias)
+// (src/fast_mimi/model.py:2745-2753; forward of the class: nn.ConvTranspose1d, then the last kernel - stride = 2
+// output frames are trimmed, causal with trim_right_ratio 1).  With one channel per group it is elementwise: on
+// frame-major activations  y[b, n, c] = w[c, n % 2] x[b, n / 2, c] + w[c, n % 2 + 2] x[b, n / 2 - 1, c]  for
+// n = 0 .. 2T-1 (the second term absent for n < 2).  FP32 in, FP32 out, HBM-bound: 4 bytes read (each x value serves
+// four outputs through L1 / L2) and 8 written per input value.
+__global__ void __launch_bounds__(256)
+upsample2_depthwise_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int B, int T,
+                           int C) {
+  const int c4 = C / 4;
+  const long long total = static_cast<long long>(B) * 2 * T * c4;
+  const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+    const int cq = static_cast<int>(i % c4);
+    long long r = i / c4;
+    const int n = static_cast<int>(r % (2 * T));
+    const long long b = r / (2 * T);
+    const int t = n >> 1, j = n & 1;
+    const float4 a = __ldg(reinterpret_cast<const float4*>(x + (b * T + t) * C) + cq);
+    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t > 0) p = __ldg(reinterpret_cast<const float4*>(x + (b * T + t - 1) * C) + cq);
+    const float* wc = w + static_cast<long long>(cq) * 16;        // four channels x four taps
+    float4 o;
+    o.x = wc[j] * a.x + wc[j + 2] * p.x;
+    o.y = wc[4 + j] * a.y + wc[4 + j + 2] * p.y;
+    o.z = wc[8 + j] * a.z + wc[8 + j + 2] * p.z;
+    o.w = wc[12 + j] * a.w + wc[12 + j + 2] * p.w;
+    reinterpret_cast<float4*>(y + (b * 2 * T + n) * C)[cq] = o;
+  }
+}
+
+int launch_upsample2_depthwise(const float* x, const float* w, float* y, int B, int T, int C, cudaStream_t st) {
+  if (B <= 0 || T <= 0) return (B == 0 || T == 0) ? 0 : -1;
+  if (C <= 0 || C % 4 != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15u) return -3;
+  const long long total = static_cast<long long>(B) * 2 * T * (C / 4);
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long want = (total + 255) / 256, cap = static_cast<long long>(sms > 0 ? sms : 1) * 8;
+  upsample2_depthwise_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, st>>>(x, w, y, B, T, C);
   return static_cast<int>(cudaGetLastError());
 }
 

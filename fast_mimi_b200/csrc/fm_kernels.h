@@ -67,7 +67,16 @@ int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, co
 int launch_conv_rows_split(const float* x, void* hi, void* lo, int B, int T, int C, int kernel, int stride,
                            cudaStream_t st);
 int launch_wait_timeout_selftest(int* status, int limit_us, int* observed, cudaStream_t st);
+// y[B, 2T, C] from x[B, T, C] by the depthwise transposed convolution of kernel 4, stride 2 (w [C, 4]), FP32.
+int launch_upsample2_depthwise(const float* x, const float* w, float* y, int B, int T, int C, cudaStream_t st);
 int launch_split_half(const float* x, void* hi, void* lo, long long n, cudaStream_t st);
+// Record-based variant (no scores in memory): candidate records from launch_linear_gemm(out_dtype 3), per-frame
+// margins in `tau` (written for the next layer by the decision kernel, for the first layer by launch_rvq_prepare).
+int launch_rvq_select_rec(const void* records, const float* codebook, float* resid, void* resid16, long long* codes,
+                          int* n_candidates, float* tau, long long rows, int n_codes, float e_max_next, float tau_rel,
+                          int* status, cudaStream_t st);
+int launch_rvq_prepare(const float* x, void* resid16, float* tau, long long rows, float e_max, float tau_rel,
+                       cudaStream_t st);
 int launch_rvq_to_half(const float* x, void* y, long long rows, cudaStream_t st);
 int launch_rvq_decode(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
                       int n_codes, int* bad_code, cudaStream_t st);

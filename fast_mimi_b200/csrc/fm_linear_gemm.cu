@@ -74,13 +74,16 @@ __device__ __forceinline__ float gelu_erf(float x) {
 }  // namespace lin
 
 struct LinearArgs {
-  const float* scale;     // [N] or null
-  const void* resid;      // [M, N] in the output's type or null
+  const float* scale;     // [N] or null             (kOut 3: |e_j|^2 of the codebook entries)
+  const void* resid;      // [M, N] in the output's type or null      (kOut 3: per-row candidate margin, [M] FP32)
   int M, N, K;
   int gelu;               // 1: exact GELU on the accumulator before scale / residual
+  uint4* records;         // kOut 3: [M, N / 64] candidate records
 };
 
-// kOut: 0 = BF16, 1 = FP16, 2 = FP32 (type of y and of the residual)
+// kOut: 0 = BF16, 1 = FP16, 2 = FP32 (type of y and of the residual); 3 = no y at all: the products are the inner
+// products x . e_j of a nearest-entry search and the epilogue reduces every 64 of them to one 16-byte record
+// {min_j d_j, 64-bit mask of the entries with d_j <= min + margin[row]},  d_j = |e_j|^2 - 2 x . e_j  (see fm_rvq.cu).
 template <int kOut>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(lin::kThreads, 1)
 linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
@@ -216,6 +219,28 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           v[c] = __uint_as_float(raw_lo[c]);
           v[32 + c] = __uint_as_float(raw_hi[c]);
         }
+        if constexpr (kOut == 3) {
+          // approximate distances of this row to entries col0 .. col0 + 63, their minimum and who is within the margin
+          const float4* q4 = reinterpret_cast<const float4*>(args.scale + col0);        // same address in every lane
+          float dmin = INFINITY;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 q = __ldg(q4 + j);
+            v[4 * j] = fmaf(-2.f, v[4 * j], q.x); v[4 * j + 1] = fmaf(-2.f, v[4 * j + 1], q.y);
+            v[4 * j + 2] = fmaf(-2.f, v[4 * j + 2], q.z); v[4 * j + 3] = fmaf(-2.f, v[4 * j + 3], q.w);
+            dmin = fminf(dmin, fminf(fminf(v[4 * j], v[4 * j + 1]), fminf(v[4 * j + 2], v[4 * j + 3])));
+          }
+          const float limit = dmin + (row_ok ? __ldg(static_cast<const float*>(args.resid) + row) : 0.f);
+          uint32_t m_lo = 0u, m_hi = 0u;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            m_lo |= (v[c] <= limit ? 1u : 0u) << c;
+            m_hi |= (v[32 + c] <= limit ? 1u : 0u) << c;
+          }
+          if (row_ok)
+            args.records[row * (args.N / 64) + (col0 >> 6)] = make_uint4(__float_as_uint(dmin), m_lo, m_hi, 0u);
+          continue;
+        }
         if (args.gelu) {
 #pragma unroll
           for (int c = 0; c < 64; ++c) v[c] = gelu_erf(v[c]);
@@ -316,9 +341,10 @@ int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale
                        int K, int in_dtype, int out_dtype, int gelu, int* status, cudaStream_t st) {
   using namespace lin;
   if (M < 0 || N <= 0 || K <= 0 || N % kBlockN != 0 || K % kBlockK != 0) return -1;
-  if (in_dtype < 0 || in_dtype > 1 || out_dtype < 0 || out_dtype > 2) return -1;
+  if (in_dtype < 0 || in_dtype > 1 || out_dtype < 0 || out_dtype > 3) return -1;
   if (M == 0) return 0;
   if (a == nullptr || w == nullptr || y == nullptr) return -1;
+  if (out_dtype == 3 && (scale == nullptr || resid == nullptr || gelu)) return -1;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y) |
        reinterpret_cast<uintptr_t>(scale) | reinterpret_cast<uintptr_t>(resid)) & 15u)
     return -3;
@@ -328,7 +354,9 @@ int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale
   if (rc != 0) return rc;
   rc = encode_2d(&tmap_w, t16, 2, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), kHalfN, kBlockK);
   if (rc != 0) return rc;
-  if (out_dtype == 2)
+  if (out_dtype == 3)      // no tiled store in this mode: a placeholder map over a
+    rc = encode_2d(&tmap_y, t16, 2, a, static_cast<uint64_t>(M), static_cast<uint64_t>(K), 32, 64);
+  else if (out_dtype == 2)
     rc = encode_2d(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), 32, 32);
   else
     rc = encode_2d(&tmap_y, t16, 2, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), 32, 64);
@@ -343,8 +371,9 @@ int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale
   const int n_pairs = total_units < max_pairs ? total_units : max_pairs;
   const int fmt = in_dtype == 1 ? 0 : 1;   // tcgen05 kind::f16 operand format: 0 = F16, 1 = BF16
   const uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, fmt, fmt, 0, 0);
-  LinearArgs args = {scale, resid, M, N, K, gelu ? 1 : 0};
-  auto kern = out_dtype == 2 ? linear_gemm_kernel<2> : (out_dtype == 1 ? linear_gemm_kernel<1> : linear_gemm_kernel<0>);
+  LinearArgs args = {scale, resid, M, N, K, gelu ? 1 : 0, out_dtype == 3 ? static_cast<uint4*>(y) : nullptr};
+  auto kern = out_dtype == 3 ? linear_gemm_kernel<3>
+                             : (out_dtype == 2 ? linear_gemm_kernel<2> : (out_dtype == 1 ? linear_gemm_kernel<1> : linear_gemm_kernel<0>));
   rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
   if (rc != 0) return rc;
   kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_y, args, total_units, idesc, status);

@@ -69,7 +69,7 @@ rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_s
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) xx += __shfl_xor_sync(0xffffffffu, xx, o);
     // relative part: FP16 rounding of both operands; absolute part: residual values below FP16's normal range
-    const float tau = tau_rel * sqrtf(xx) * e_max + 3.1e-5f * e_max;
+    const float tau = tau_rel * sqrtf(xx) * e_max + 3.1e-5f * e_max;      // == rvq_margin below
 
     // pass A: approximate distances of this lane's entries (kept in registers) and their minimum.  Lane l holds
     // entries 128 * it + 4 * l + e, it = 0 .. n_codes / 128 - 1, e = 0 .. 3.
@@ -152,6 +152,126 @@ rvq_select_kernel(const void* __restrict__ scores, const float* __restrict__ e_s
       // candidate and the code above is meaningless.  Say so instead of emitting entry 0 silently.
       if (n_cand == 0 && status != nullptr) atomicMax(status, static_cast<int>(kErrNonFinite));
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same search without the scores' round trip through memory: the inner-product GEMM's epilogue (linear kernel,
+// record mode) reduces every 64 entries of a frame to one 16-byte record {minimum approximate distance, 64-bit mask of
+// the entries within the frame's margin of that minimum}, 32 records per frame for 2048 entries (512 B instead of
+// 4 KB of FP16 scores).  An entry within the margin of the GLOBAL minimum is within the margin of its own group's
+// minimum, so the union of the masks of the groups whose minimum is within the margin of the global one contains every
+// true candidate; the extra ones only cost an exact evaluation each.  The margin of a frame depends on its residual
+// norm, which the previous layer's decision kernel (or rvq_prepare_kernel before the first layer) leaves in `tau`.
+__device__ __forceinline__ float rvq_margin(float xx, float e_max, float tau_rel) {
+  // relative part: FP16 rounding of both operands; absolute part: residual values below FP16's normal range
+  return tau_rel * sqrtf(xx) * e_max + 3.1e-5f * e_max;
+}
+
+__global__ void __launch_bounds__(rvq::kWarps * 32)
+rvq_select_rec_kernel(const uint4* __restrict__ records, const float* __restrict__ codebook, float* __restrict__ resid,
+                      uint16_t* __restrict__ resid16, long long* __restrict__ codes, int* __restrict__ n_candidates,
+                      float* __restrict__ tau, long long rows, int n_groups, float e_max_next, float tau_rel,
+                      int* __restrict__ status) {
+  using namespace rvq;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+  for (long long row = warp0; row < rows; row += stride) {
+    float x[8];
+    {
+      const float4* xr = reinterpret_cast<const float4*>(resid + row * kDim + lane * 8);
+      const float4 a = xr[0], b = xr[1];
+      x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+    }
+    // this lane's group (entries 64 * lane .. 64 * lane + 63): its minimum and its mask
+    uint4 rec = make_uint4(__float_as_uint(INFINITY), 0u, 0u, 0u);
+    if (lane < n_groups) rec = records[row * n_groups + lane];
+    const float gmin = __uint_as_float(rec.x);
+    float d_min = gmin;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d_min = fminf(d_min, __shfl_xor_sync(0xffffffffu, d_min, o));
+    const float limit = d_min + tau[row];
+    unsigned long long mine = gmin <= limit ? (static_cast<unsigned long long>(rec.z) << 32) | rec.y : 0ull;
+
+    float best = INFINITY;
+    int best_j = 0, n_cand = 0;
+    unsigned lanes = __ballot_sync(0xffffffffu, mine != 0ull);
+    while (lanes != 0u) {
+      const int src = __ffs(lanes) - 1;
+      lanes &= lanes - 1u;
+      unsigned long long bits = __shfl_sync(0xffffffffu, mine, src);
+      while (bits != 0ull) {
+        const int bit = __ffsll(static_cast<long long>(bits)) - 1;
+        bits &= bits - 1ull;
+        const int j = src * 64 + bit;
+        const float4* er = reinterpret_cast<const float4*>(codebook + static_cast<size_t>(j) * kDim + lane * 8);
+        const float4 a = __ldg(er), b = __ldg(er + 1);
+        const float ev[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float t = x[k] - ev[k];
+          acc = fmaf(t, t, acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        ++n_cand;
+        if (acc < best || (acc == best && j < best_j)) {      // ties go to the lower index (argmin's rule)
+          best = acc;
+          best_j = j;
+        }
+      }
+    }
+    {
+      const float4* er = reinterpret_cast<const float4*>(codebook + static_cast<size_t>(best_j) * kDim + lane * 8);
+      const float4 a = __ldg(er), b = __ldg(er + 1);
+      const float ev[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      float xx = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        x[k] -= ev[k];
+        xx = fmaf(x[k], x[k], xx);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) xx += __shfl_xor_sync(0xffffffffu, xx, o);
+      float4* xw = reinterpret_cast<float4*>(resid + row * kDim + lane * 8);
+      xw[0] = make_float4(x[0], x[1], x[2], x[3]);
+      xw[1] = make_float4(x[4], x[5], x[6], x[7]);
+      *reinterpret_cast<uint4*>(resid16 + row * kDim + lane * 8) =
+          make_uint4(Pack16<__half>::pack(x[0], x[1]), Pack16<__half>::pack(x[2], x[3]), Pack16<__half>::pack(x[4], x[5]),
+                     Pack16<__half>::pack(x[6], x[7]));
+      if (lane == 0) tau[row] = rvq_margin(xx, e_max_next, tau_rel);      // the next layer's margin for this frame
+    }
+    if (lane == 0) {
+      codes[row] = best_j;
+      if (n_candidates != nullptr) n_candidates[row] = n_cand;
+      if (n_cand == 0 && status != nullptr) atomicMax(status, static_cast<int>(kErrNonFinite));
+    }
+  }
+}
+
+// Before the first layer: FP16 copy of the residual and every frame's candidate margin (one warp per frame).
+__global__ void __launch_bounds__(rvq::kWarps * 32)
+rvq_prepare_kernel(const float* __restrict__ x, uint16_t* __restrict__ resid16, float* __restrict__ tau, long long rows,
+                   float e_max, float tau_rel) {
+  using namespace rvq;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  const long long stride = static_cast<long long>(gridDim.x) * kWarps;
+  for (long long row = warp0; row < rows; row += stride) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * kDim + lane * 8);
+    const float4 a = xr[0], b = xr[1];
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float xx = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) xx = fmaf(v[k], v[k], xx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) xx += __shfl_xor_sync(0xffffffffu, xx, o);
+    *reinterpret_cast<uint4*>(resid16 + row * kDim + lane * 8) =
+        make_uint4(Pack16<__half>::pack(v[0], v[1]), Pack16<__half>::pack(v[2], v[3]), Pack16<__half>::pack(v[4], v[5]),
+                   Pack16<__half>::pack(v[6], v[7]));
+    if (lane == 0) tau[row] = rvq_margin(xx, e_max, tau_rel);
   }
 }
 
@@ -240,6 +360,34 @@ int launch_rvq_select(const void* scores, int scores_fp16, const float* e_sq, co
   else
     rvq_select_kernel<false><<<grid, rvq::kWarps * 32, 0, st>>>(scores, e_sq, codebook, resid, static_cast<uint16_t*>(resid16),
                                                                codes, n_candidates, rows, n_codes, e_max, tau_rel, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_rvq_select_rec(const void* records, const float* codebook, float* resid, void* resid16, long long* codes,
+                          int* n_candidates, float* tau, long long rows, int n_codes, float e_max_next, float tau_rel,
+                          int* status, cudaStream_t st) {
+  if (rows < 0 || n_codes <= 0 || n_codes % 64 != 0 || n_codes > 2048 || !(e_max_next >= 0.f) || !(tau_rel >= 0.f)) return -1;
+  if (rows == 0) return 0;
+  if (records == nullptr || codebook == nullptr || resid == nullptr || resid16 == nullptr || codes == nullptr || tau == nullptr)
+    return -1;
+  if ((reinterpret_cast<uintptr_t>(records) | reinterpret_cast<uintptr_t>(codebook) | reinterpret_cast<uintptr_t>(resid) |
+       reinterpret_cast<uintptr_t>(resid16)) & 15u)
+    return -3;
+  const int grid = grid_for((rows + rvq::kWarps - 1) / rvq::kWarps, 8);
+  rvq_select_rec_kernel<<<grid, rvq::kWarps * 32, 0, st>>>(static_cast<const uint4*>(records), codebook, resid,
+                                                          static_cast<uint16_t*>(resid16), codes, n_candidates, tau, rows,
+                                                          n_codes / 64, e_max_next, tau_rel, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_rvq_prepare(const float* x, void* resid16, float* tau, long long rows, float e_max, float tau_rel,
+                       cudaStream_t st) {
+  if (rows < 0 || !(e_max >= 0.f) || !(tau_rel >= 0.f)) return -1;
+  if (rows == 0) return 0;
+  if (x == nullptr || resid16 == nullptr || tau == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(resid16)) & 15u) return -3;
+  rvq_prepare_kernel<<<grid_for((rows + rvq::kWarps - 1) / rvq::kWarps, 8), rvq::kWarps * 32, 0, st>>>(
+      x, static_cast<uint16_t*>(resid16), tau, rows, e_max, tau_rel);
   return static_cast<int>(cudaGetLastError());
 }
 

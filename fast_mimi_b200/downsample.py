@@ -1,4 +1,9 @@
-"""Drop-in for the reference's ``MimiModel.downsample`` (the stride-2 convolution between the encoder transformer and
+"""Drop-ins for the two stride-2 convolutions around the quantiser.
+
+``MimiUpsampleB200`` replaces ``MimiModel.upsample`` (``MimiConvTranspose1d(512, 512, kernel 4, stride 2, groups=512,
+bias=False)``, src/fast_mimi/model.py:2745-2753): one channel per group makes it elementwise.
+
+``MimiDownsampleB200`` replaces ``MimiModel.downsample`` (the stride-2 convolution between the encoder transformer and
 the quantiser: ``MimiConv1d(512, 512, kernel 4, stride 2, bias=False, pad_mode="replicate")``,
 src/fast_mimi/model.py:2734-2744) on B200.
 
@@ -50,3 +55,28 @@ class MimiDownsampleB200(nn.Module):
             raise RuntimeError("MimiDownsampleB200 runs on a CUDA device only; there is no CPU path")
         y = self.frames(hidden_states.transpose(1, 2))
         return y.transpose(1, 2).to(hidden_states.dtype)
+
+
+class MimiUpsampleB200(nn.Module):
+    def __init__(self, convtr: nn.Module) -> None:
+        """``convtr``: a module with the reference's ``MimiConvTranspose1d`` attributes (``conv`` =
+        ``nn.ConvTranspose1d``, ``padding_left`` / ``padding_right``); its weight is shared, not copied."""
+        super().__init__()
+        inner = convtr.conv
+        c = inner.in_channels
+        if (inner.bias is not None or inner.groups != c or inner.out_channels != c or inner.kernel_size[0] != 4
+                or inner.stride[0] != 2):
+            raise ValueError("only Mimi's depthwise, bias-free transposed convolution (kernel 4, stride 2) is built")
+        if getattr(convtr, "padding_left", 0) != 0 or getattr(convtr, "padding_right", 2) != 2:
+            raise ValueError("only the causal trimming of Mimi's configuration (two trailing frames) is built")
+        self.conv = inner
+
+    def frames(self, x: torch.Tensor) -> torch.Tensor:
+        """``x [B, T, C]`` (frame-major) -> ``[B, 2T, C]`` float32."""
+        w = self.conv.weight.detach().float().reshape(self.conv.in_channels, 4).contiguous()
+        return ops.upsample2(x.float().contiguous(), w)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        if not hidden_states.is_cuda:
+            raise RuntimeError("MimiUpsampleB200 runs on a CUDA device only; there is no CPU path")
+        return self.frames(hidden_states.transpose(1, 2)).transpose(1, 2).to(hidden_states.dtype)

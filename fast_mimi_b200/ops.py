@@ -260,6 +260,27 @@ def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtyp
     return out
 
 
+def band_attention_chunk(q, k, v, *, window=250, scale=0.125, out=None, status=None):
+    """Banded attention of ``q [B,Tq,512]`` (bf16, rotated) against ``k, v [B,Tk,512]`` with ``Tk >= Tq``: the last
+    ``Tq`` key rows are the queries' own frames, the rows before them older (cached) ones.  Returns ``[B,Tq,512]``."""
+    lib = _native.load()
+    _need(q.dim() == 3 and k.dim() == 3, "q and k must be [B, T, 512]")
+    B, Tq, _ = q.shape
+    Tk = k.shape[1]
+    _need(Tk >= Tq and k.shape[0] == B, "k must hold at least the queries' own frames")
+    _check_frames(q, "q", torch.bfloat16)
+    _check_frames(k, "k", torch.bfloat16, B * Tk)
+    _need(v.dtype in _VALUE_CODES, "v must be float16 or bfloat16")
+    _check_frames(v, "v", v.dtype, B * Tk)
+    if out is None:
+        out = torch.empty(q.shape, dtype=v.dtype, device=q.device)
+    _check_frames(out, "out", v.dtype, B * Tq)
+    rc = lib.fm_band_attn_chunk_bf16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, Tq, Tk, window, scale,
+                                     _VALUE_CODES[v.dtype], _status_ptr(status, q), _stream())
+    _native.check(rc, "fm_band_attn_chunk_bf16")
+    return out
+
+
 def attention_fused(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtype=torch.float16, out=None, status=None):
     """Projection + RoPE + banded attention in one kernel for clips of 128 < T <= 256 frames: ``x [B,T,512]`` ->
     ``[B,T,512]`` value_dtype, no q / k / v workspace (they stay in shared and tensor memory)."""
@@ -513,13 +534,13 @@ class RVQCodebooks:
         self.layers, self.entries = codebooks.shape[0], codebooks.shape[1]
 
 
-def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates=False, scores_dtype=torch.float16,
-               status=None):
+def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates=False, scores_dtype=None, status=None):
     """Codes ``[layers, rows]`` int64 of the residual quantiser stack for ``x [rows, 256]`` float32 (the output
     of the branch's ``input_proj``).  Per layer: inner products with all entries on the tensor core (FP16
     operands) pre-select, the exact FP32 distance decides among the candidates, the chosen entry is subtracted.
-    The scores make one round trip through memory, in FP16 by default (half the traffic; the candidate margin
-    accounts for their rounding).  ``x`` is not modified."""
+    By default (``scores_dtype=None``) the products never reach memory: the GEMM's epilogue reduces every 64 of them
+    to a 16-byte candidate record.  ``scores_dtype=torch.float16 / torch.float32`` selects the older form in which the
+    scores make one round trip through memory in that type.  ``x`` is not modified."""
     lib = _native.load()
     _need(x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] == RVQ_DIM, "x must be CUDA float32 [rows, 256]")
     layers = books.layers if num_quantizers is None else int(num_quantizers)
@@ -527,17 +548,34 @@ def rvq_encode(x, books: RVQCodebooks, num_quantizers=None, *, return_candidates
     rows = x.shape[0]
     resid = x.contiguous().clone()
     resid16 = torch.empty(rows, RVQ_DIM, dtype=torch.float16, device=x.device)
-    _need(scores_dtype in RVQ_TAU_REL, "scores_dtype must be float16 or float32")
-    scores = torch.empty(rows, books.entries, dtype=scores_dtype, device=x.device)
     codes = torch.empty(layers, rows, dtype=torch.int64, device=x.device)
     cand = torch.empty(layers, rows, dtype=torch.int32, device=x.device) if return_candidates else None
+    st = _status_ptr(status, x)
+    if scores_dtype is None:
+        tau_rel = RVQ_TAU_REL[torch.float32]          # FP32 accumulators feed the comparison directly
+        tau = torch.empty(rows, dtype=torch.float32, device=x.device)
+        records = torch.empty(rows, books.entries // 64, 4, dtype=torch.int32, device=x.device)
+        _native.check(lib.fm_rvq_prepare_f32(resid.data_ptr(), resid16.data_ptr(), tau.data_ptr(), rows, books.e_max[0],
+                                             tau_rel, _stream()), "fm_rvq_prepare_f32")
+        for l in range(layers):
+            rc = lib.fm_rvq_candidates_f16(resid16.data_ptr(), books.half[l].data_ptr(), books.sq[l].data_ptr(),
+                                           tau.data_ptr(), records.data_ptr(), rows, books.entries, st, _stream())
+            _native.check(rc, "fm_rvq_candidates_f16")
+            e_next = books.e_max[l + 1] if l + 1 < layers else 0.0
+            rc = lib.fm_rvq_select_rec_f32(records.data_ptr(), books.vectors[l].data_ptr(), resid.data_ptr(),
+                                           resid16.data_ptr(), codes[l].data_ptr(),
+                                           cand[l].data_ptr() if cand is not None else None, tau.data_ptr(), rows,
+                                           books.entries, e_next, tau_rel, st, _stream())
+            _native.check(rc, "fm_rvq_select_rec_f32")
+        return (codes, cand) if return_candidates else codes
+    _need(scores_dtype in RVQ_TAU_REL, "scores_dtype must be None, float16 or float32")
+    scores = torch.empty(rows, books.entries, dtype=scores_dtype, device=x.device)
     _native.check(lib.fm_rvq_to_half(resid.data_ptr(), resid16.data_ptr(), rows, _stream()), "fm_rvq_to_half")
     for l in range(layers):
         linear(resid16, books.half[l], out_dtype=scores_dtype, out=scores, status=status)
         rc = lib.fm_rvq_select_f32(scores.data_ptr(), _OUT_CODES[scores_dtype], books.sq[l].data_ptr(), books.vectors[l].data_ptr(), resid.data_ptr(),
                                    resid16.data_ptr(), codes[l].data_ptr(), cand[l].data_ptr() if cand is not None else None,
-                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL[scores_dtype], _status_ptr(status, x),
-                                   _stream())
+                                   rows, books.entries, books.e_max[l], RVQ_TAU_REL[scores_dtype], st, _stream())
         _native.check(rc, "fm_rvq_select_f32")
     return (codes, cand) if return_candidates else codes
 
@@ -584,6 +622,19 @@ def downsample_conv(x, w_parts, *, kernel=4, stride=2, status=None):
     y2 = linear(lo, w_hi, residual=y, out_dtype=torch.float32, status=status)
     y = linear(hi, w_hi, residual=y2, out_dtype=torch.float32, out=y, status=status)
     return y.view(B, t_out, w_hi.shape[0])
+
+
+def upsample2(x, weight):
+    """The depthwise transposed convolution (kernel 4, stride 2, trailing two frames trimmed) that precedes the decoder
+    transformer, on frame-major activations: ``x [B, T, C]`` float32, ``weight [C, 4]`` float32 -> ``[B, 2T, C]``."""
+    lib = _native.load()
+    _need(x.is_cuda and x.dtype == torch.float32 and x.dim() == 3 and x.is_contiguous(), "x must be contiguous CUDA float32 [B, T, C]")
+    B, T, C = x.shape
+    _need(weight.is_cuda and weight.dtype == torch.float32 and weight.is_contiguous() and tuple(weight.shape) == (C, 4)
+          and C % 4 == 0, f"weight must be contiguous CUDA float32 [{C}, 4]")
+    y = torch.empty(B, 2 * T, C, dtype=torch.float32, device=x.device)
+    _native.check(lib.fm_upsample2_f32(x.data_ptr(), weight.data_ptr(), y.data_ptr(), B, T, C, _stream()), "fm_upsample2_f32")
+    return y
 
 
 def rvq_decode(codes, books: RVQCodebooks):

@@ -55,6 +55,13 @@ int fm_qkv_rope_bf16(const void* x, const void* w_qkv, const float* cos, const f
 int fm_band_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, int B, int T,
                               int window, float scale, int value_dtype, int* status, void* stream);
 
+/* Banded attention of Tq query frames against Tk >= Tq key / value frames whose last Tq rows are the queries' own
+ * frames and whose first Tk - Tq rows are older (cached) frames: the masked SDPA of a cached call with
+ * query_offset - key_offset = Tk - Tq (src/fast_mimi/model.py:1672-1677, :2194-2205) on rotated q [B,Tq,512] BF16,
+ * k [B,Tk,512] BF16, v [B,Tk,512] (value type) -> out [B,Tq,512].  Tk == Tq is fm_band_attn_prefill_bf16. */
+int fm_band_attn_chunk_bf16(const void* q, const void* k, const void* v, void* out, int B, int Tq, int Tk, int window,
+                            float scale, int value_dtype, int* status, void* stream);
+
 /* The same computation as fm_attention_prefill_bf16 in ONE kernel for clips of 128 < T <= 256 frames (Mimi's
  * 10 s clips): x and W_qkv in, attention output out, the rotated q, k, v never reach memory, so no workspace.
  * Replaces src/fast_mimi/model.py:1897-1914 + :1627-1688 + :1860-1868 for such clips (the reference's own fused
@@ -136,12 +143,38 @@ int fm_rvq_select_f32(const void* scores, int scores_dtype, const float* e_sq, c
  * [C_out, kernel * C_in] (three products: hi W_hi + hi W_lo + lo W_hi, FP32 residual chaining). */
 int fm_conv_rows_split(const float* x, void* hi, void* lo, int B, int T, int C, int kernel, int stride, void* stream);
 
+/* The stride-2 upsampling that precedes the decoder transformer (MimiModel.upsample: MimiConvTranspose1d(512, 512,
+ * kernel 4, stride 2, groups 512, no bias), src/fast_mimi/model.py:2745-2753; its forward trims the last two output
+ * frames): x [B, T, C] FP32 frame-major, w [C, 4] FP32 (the ConvTranspose1d weight [C, 1, 4]) -> y [B, 2T, C] FP32,
+ * y[b, n, c] = w[c, n % 2] x[b, n / 2, c] + w[c, n % 2 + 2] x[b, n / 2 - 1, c]. */
+int fm_upsample2_f32(const float* x, const float* w, float* y, int B, int T, int C, void* stream);
+
 /* x = hi + lo, both FP16 (hi = round(x), lo = round(x - hi)), n a multiple of 8 values: the operands of an
  * FP32-grade product on the FP16 tensor core (hi W_hi + hi W_lo + lo W_hi via fm_linear_f16 with FP32 residual
  * chaining).  Used for the quantiser's 1 x 1 input / output projections (nn.Conv1d(kernel 1, no bias),
  * src/fast_mimi/model.py:2392-2406, applied at :2417 and :2443), whose results decide code indices and must
  * therefore keep FP32 accuracy. */
 int fm_split_half(const float* x, void* hi, void* lo, long long n, void* stream);
+
+/* The same layer without the scores' round trip through memory (replaces the same reference lines as
+ * fm_rvq_select_f32: src/fast_mimi/model.py:2277-2291, :2420-2427), three calls:
+ *   fm_rvq_prepare_f32     before the first layer: FP16 copy of x [rows, 256] and every frame's candidate margin
+ *                          tau[row] = tau_rel * |x| * e_max + 3.1e-5 * e_max (e_max of the FIRST layer's codebook)
+ *   fm_rvq_candidates_f16  the inner products residual16 [rows, 256] x codebook16 [n_codes, 256]^T on the tensor core
+ *                          (FP16 operands); the epilogue turns every 64 of them into one 16-byte record {minimum of
+ *                          d_j = e_sq[j] - 2 x.e_j, 64-bit mask of the entries with d_j <= minimum + tau[row]}:
+ *                          records [rows, n_codes / 64] x 16 B; n_codes a multiple of 256, at most 2048
+ *   fm_rvq_select_rec_f32  exact FP32 decision among the entries flagged in the groups whose minimum is within tau of
+ *                          the frame's global minimum (lowest index on ties), residual update, FP16 copy, and the
+ *                          frame's margin for the NEXT layer (e_max_next = that layer's max |e_j|; 0 after the last)
+ * With FP32 accumulation in the GEMM and no FP16 storage of the scores, tau_rel = 4.5e-3 covers the operand rounding. */
+int fm_rvq_prepare_f32(const float* x, void* residual16, float* tau, long long rows, float e_max, float tau_rel,
+                       void* stream);
+int fm_rvq_candidates_f16(const void* residual16, const void* codebook16, const float* e_sq, const float* tau,
+                          void* records, long long rows, int n_codes, int* status, void* stream);
+int fm_rvq_select_rec_f32(const void* records, const float* codebook, float* residual, void* residual16, long long* codes,
+                          int* n_candidates, float* tau, long long rows, int n_codes, float e_max_next, float tau_rel,
+                          int* status, void* stream);
 
 /* FP16 copy of [rows, 256] FP32 values (the residual before the first layer). */
 int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream);

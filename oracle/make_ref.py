@@ -2,6 +2,9 @@
 
     python oracle/make_ref.py [/path/to/reference/checkout]
 
+Without an argument the checkout is looked for in ``$FAST_MIMI_REFERENCE`` and then in a directory ``reference``
+beside this repository.
+
 The reference (a pure-Python package over PyTorch) is copied file by file from ``<checkout>/src/fast_mimi`` into
 ``oracle/_ref/fast_mimi``.  ``oracle/_ref`` is ignored by git, so nothing of it enters this repository's history;
 it exists only where this script has been run, and it travels with the working tree like the built shared
@@ -18,8 +21,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 
 
-def make(checkout: str = "/root/reference") -> str | None:
-    src = os.path.join(checkout, "src", "fast_mimi")
+def default_checkout() -> str:
+    return os.environ.get("FAST_MIMI_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def make(checkout: str | None = None) -> str | None:
+    src = os.path.join(checkout or default_checkout(), "src", "fast_mimi")
     if not os.path.isdir(src):
         return None
     dst = os.path.join(DEST, "fast_mimi")

@@ -273,6 +273,28 @@ def downsample():
     save("downsample.npz", **arrays)
 
 
+def upsample():
+    """The reference's stride-2 ``upsample`` transposed convolution (MimiModel.upsample, model.py:2745-2753) on seeded
+    frames; outputs at a few frames."""
+    from fast_mimi.model import MimiConvTranspose1d
+    cfg = MimiConfig()
+    torch.manual_seed(52)
+    convtr = MimiConvTranspose1d(cfg, cfg.hidden_size, cfg.hidden_size, 4, stride=2, bias=False,
+                                 groups=cfg.upsample_groups).eval()
+    with torch.no_grad():
+        convtr.conv.weight.copy_(torch.randn(convtr.conv.weight.shape) / 2)
+    arrays = dict(seed=52, weight_probe=convtr.conv.weight[:3, 0])
+    for t in (63, 125, 1):
+        x = torch.randn(2, t, cfg.hidden_size)
+        with torch.inference_mode():
+            y = convtr(x.transpose(1, 2)).transpose(1, 2)             # [2, 2t, 512]
+        rows = np.array(sorted(set([0, 1, 2, 3, y.shape[1] // 2, y.shape[1] - 2, y.shape[1] - 1]) & set(range(y.shape[1]))))
+        arrays[f"rows{t}"] = rows
+        arrays[f"out{t}"] = y[:, rows]
+        arrays[f"frames{t}"] = y.shape[1]
+    save("upsample.npz", **arrays)
+
+
 def rvq_codes():
     """Residual quantiser stack of the reference (7 layers, 2048 x 256 codebooks, 1x1 input projection) on seeded
     embeddings [2, 512, 40]: codes, and the decoded sum before the output projection at a few frames."""
@@ -320,3 +342,4 @@ if __name__ == "__main__":
         end_to_end_codes(seconds)
     rvq_codes()
     downsample()
+    upsample()

@@ -1,5 +1,6 @@
-"""The stride-2 downsampling convolution between the encoder transformer and the quantiser on the GPU
-(row gather + split-precision tensor-core products) vs the reference's outputs (golden fixture) and the CPU oracle."""
+"""The two stride-2 convolutions around the quantiser on the GPU: the downsampling convolution after the encoder
+transformer (row gather + split-precision tensor-core products) and the depthwise transposed convolution before the
+decoder transformer (elementwise), vs the reference's outputs (golden fixtures) and the CPU oracle."""
 from __future__ import annotations
 
 import pytest
@@ -66,3 +67,35 @@ def test_downsample_module_keeps_the_reference_call_shape():
         mod(x, padding_cache=object())
     with pytest.raises(RuntimeError):
         mod(x.cpu())
+
+
+def test_upsample_matches_the_reference_fixture_and_the_oracle():
+    import fast_mimi_b200 as fm
+    g = load_golden("upsample.npz")
+    torch.manual_seed(int(g["seed"]))
+    torch.nn.ConvTranspose1d(512, 512, 4, 2, groups=512, bias=False)
+    weight = torch.randn(512, 1, 4) / 2
+    w = weight.reshape(512, 4).contiguous().cuda()
+    for t in (63, 125, 1):
+        x = torch.randn(2, t, 512)
+        y = fm.ops.upsample2(x.cuda(), w).cpu()
+        assert y.shape == (2, 2 * t, 512)
+        assert float((y[:, g[f"rows{t}"]] - g[f"out{t}"]).abs().max()) < 1e-6      # two FP32 products and one add
+        assert float((y - O.upsample_conv(x, weight)).abs().max()) < 1e-6
+
+
+def test_upsample_module_keeps_the_reference_call_shape():
+    import types
+    import fast_mimi_b200 as fm
+    convtr = torch.nn.ConvTranspose1d(512, 512, 4, 2, groups=512, bias=False).cuda()
+    ref = types.SimpleNamespace(conv=convtr, padding_left=0, padding_right=2)
+    mod = fm.MimiUpsampleB200(ref)
+    x = torch.randn(3, 512, 40, device="cuda")
+    y = mod(x)
+    want = O.upsample_conv(x.cpu().transpose(1, 2), convtr.weight.detach().cpu()).transpose(1, 2)
+    assert y.shape == (3, 512, 80)
+    assert float((y.cpu() - want).abs().max()) < 1e-6
+    with pytest.raises(RuntimeError):
+        mod(x.cpu())
+    with pytest.raises(ValueError):
+        fm.MimiUpsampleB200(types.SimpleNamespace(conv=torch.nn.ConvTranspose1d(512, 512, 4, 2, bias=False)))

@@ -27,11 +27,13 @@ def test_rvq_codes_match_the_reference_fixture():
     codes, cand = fm.ops.rvq_encode(x.cuda(), gb, return_candidates=True)
     assert torch.equal(codes.cpu().view(7, 2, 40), g["codes"])
     assert int(cand.min()) >= 1 and float(cand.float().mean()) < 16       # a handful of exact evaluations per frame
+    for dt in (torch.float16, torch.float32):                               # the forms with the scores in memory
+        assert torch.equal(fm.ops.rvq_encode(x.cuda(), gb, scores_dtype=dt).cpu().view(7, 2, 40), g["codes"])
     dec = fm.ops.rvq_decode(codes, gb).cpu().view(2, 40, 256).permute(0, 2, 1)
     assert torch.equal(dec[:, :, ::13], g["quantized_probe"])             # ordered FP32 adds: bit-exact
 
 
-@pytest.mark.parametrize("scores_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("scores_dtype", [None, torch.float16, torch.float32])      # None: candidate records, no scores in memory
 @pytest.mark.parametrize("rows,layers", [(1, 8), (257, 3), (6000, 8)])
 def test_rvq_codes_match_the_oracle(rows, layers, scores_dtype):
     """Frame-level identity (all layers' codes equal) against the CPU oracle; inputs scaled so that the later

@@ -105,6 +105,21 @@ def test_downsample_conv_matches_reference():
         assert (y[:, g[f"rows{t}"]] - g[f"out{t}"]).abs().max() < TOL
 
 
+def test_upsample_conv_matches_reference():
+    """The oracle's stride-2 transposed convolution against the reference's MimiConvTranspose1d (depthwise, causal
+    trimming, no bias)."""
+    g = load_golden("upsample.npz")
+    torch.manual_seed(int(g["seed"]))
+    torch.nn.ConvTranspose1d(512, 512, 4, 2, groups=512, bias=False)   # the reference module's own initialisation draws first
+    weight = torch.randn(512, 1, 4) / 2
+    assert torch.equal(weight[:3, 0], g["weight_probe"])
+    for t in (63, 125, 1):
+        x = torch.randn(2, t, 512)
+        y = O.upsample_conv(x, weight)
+        assert y.shape[1] == int(g[f"frames{t}"]) == 2 * t
+        assert (y[:, g[f"rows{t}"]] - g[f"out{t}"]).abs().max() < TOL
+
+
 def test_ring_decode_260_matches_reference():
     g = load_golden("ring_decode_260.npz")
     wq, wk, wv, wo = regen_projections(int(g["seed"]))

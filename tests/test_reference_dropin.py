@@ -129,3 +129,54 @@ def test_chunked_streaming_encode_through_the_reference_model(swap):
           f"stock streaming vs the reference's offline CPU codes {_frame_agreement(stock, offline):.4f}")
     assert ours.shape == stock.shape == (1, 8, 150)
     assert _frame_agreement(ours, stock) >= 0.995
+
+
+@pytest.mark.gpu
+def test_streaming_with_the_reference_own_cache_object():
+    """use_streaming=True without handing in a ring: MimiTransformerModel.forward creates a MimiKVCache by itself
+    (src/fast_mimi/model.py:2166-2170) and the installed modules must work with it through update()."""
+    import fast_mimi_b200 as fm
+    model = _reference_model("cuda")
+    audio = synthetic_audio(seconds=12).cuda()
+    frames = [30, 2, 70, 1, 47]
+
+    def stream():
+        kv, pc, out, a = None, None, [], 0
+        for n in frames:
+            res = model.encode(audio[:, :, a * 1920:(a + n) * 1920], num_quantizers=8, encoder_past_key_values=kv,
+                               padding_cache=pc, use_streaming=True)
+            kv, pc = res.encoder_past_key_values, res.padding_cache
+            out.append(res.audio_codes)
+            a += n
+        return torch.cat(out, dim=-1).cpu(), kv
+
+    with torch.inference_mode():
+        stock, _ = stream()
+        fm.install(model.encoder_transformer)
+        ours, kv = stream()
+    fm.check_status()
+    assert isinstance(kv, MimiKVCache) and kv.get_seq_length() == 300
+    print(f"[streaming with the reference's MimiKVCache] code-frame agreement with stock: {_frame_agreement(ours, stock):.4f}")
+    assert _frame_agreement(ours, stock) >= 0.995
+
+
+@pytest.mark.gpu
+def test_decode_through_the_reference_model_with_the_native_chain():
+    """The decoder side inside the reference's MimiModel.decode (src/fast_mimi/model.py:3139-3220): quantiser decode,
+    upsample and the eight decoder-transformer layers on this library's kernels, the SEANet decoder the reference's.
+    Waveform against the stock model on the same GPU (FP32, TF32 off) for the reference's CPU codes of 5 s of audio."""
+    import fast_mimi_b200 as fm
+    from oracle import mimi_attention_oracle as O
+    model = _reference_model("cuda")
+    codes = load_golden("e2e_codes_5s.npz")["codes"].cuda()
+    with torch.inference_mode():
+        stock = model.decode(codes).audio_values.cpu()
+        fm.install_layers(model.decoder_transformer)
+        model.upsample = fm.MimiUpsampleB200(model.upsample)
+        model.quantizer.decode = fm.MimiSplitRVQB200.from_reference(model.quantizer).decode
+        ours = model.decode(codes).audio_values.cpu()
+    fm.check_status()
+    err = O.rel_l2(ours, stock)
+    print(f"[reference MimiModel.decode, native quantiser decode + upsample + decoder transformer] waveform rel-L2 vs stock: {err:.2e}")
+    assert ours.shape == stock.shape
+    assert err < 2e-3
