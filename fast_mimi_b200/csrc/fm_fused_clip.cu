@@ -205,9 +205,13 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
   if (skip) {
     // a previous kernel already reported an error through this status word: do nothing
   } else if (warp == kIssueWarp0) {
-    // ------------------------------------------------------------ W loads (one thread per CTA)
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_w);
+    // ------------------------------------------------------------ W loads
+    // In all four issuing warps the 32 lanes walk the loop together and one elected lane issues copies, MMAs and
+    // commits: warp-uniform control flow keeps descriptors in uniform registers, and a wait / few MMAs / commit
+    // sequence issues a third faster than from a single lane under a lane test.
+    {
+      const bool one = elect_one();
+      if (one) tma_prefetch_desc(&tmap_w);
       int stage = 0;
       uint32_t phase = 0;
       for (int g = 0; g < n_heads_total; ++g) {
@@ -219,31 +223,37 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         const int r2 = leader ? 512 + h * 64 : 1024 + h * 64 + 32;
         for (int kc = 0; kc < kKChunks; ++kc) {
           mbar_wait(&sh->w_empty[stage], phase ^ 1u, ctl, status, kErrWaitConsumer);
-          if (leader) mbar_arrive_expect_tx(&sh->w_full[stage], 2 * kWStageBytes);
           uint8_t* dst = smem_w + stage * kWStageBytes;
-          tma_load_2d_pair(dst, &tmap_w, &sh->w_full[stage], kc * 64, r0);
-          tma_load_2d_pair(dst + kWBoxBytes, &tmap_w, &sh->w_full[stage], kc * 64, r1);
-          tma_load_2d_pair(dst + 2 * kWBoxBytes, &tmap_w, &sh->w_full[stage], kc * 64, r2);
+          if (one) {
+            if (leader) mbar_arrive_expect_tx(&sh->w_full[stage], 2 * kWStageBytes);
+            tma_load_2d_pair(dst, &tmap_w, &sh->w_full[stage], kc * 64, r0);
+            tma_load_2d_pair(dst + kWBoxBytes, &tmap_w, &sh->w_full[stage], kc * 64, r1);
+            tma_load_2d_pair(dst + 2 * kWBoxBytes, &tmap_w, &sh->w_full[stage], kc * 64, r2);
+          }
           if (++stage == kWStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == kIssueWarp0 + 1) {
-    // ------------------------------------------------------------ x loads (one thread per CTA)
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_x);
+    // ------------------------------------------------------------ x loads
+    {
+      const bool one = elect_one();
+      if (one) tma_prefetch_desc(&tmap_x);
       for (int n = 0; n < n_local; ++n) {
         const int clip = pair + n * n_pairs;
         for (int kc = 0; kc < kKChunks; ++kc) {
           if (n > 0) mbar_wait(&sh->x_empty[kc], static_cast<uint32_t>(n - 1) & 1u, ctl, status, kErrWaitMma);
-          if (leader) mbar_arrive_expect_tx(&sh->x_full[kc], 2 * kXChunkBytes);
-          tma_load_3d_pair(smem_x + kc * kXChunkBytes, &tmap_x, &sh->x_full[kc], kc * 64, static_cast<int>(rank) * kTile, clip);
+          if (one) {
+            if (leader) mbar_arrive_expect_tx(&sh->x_full[kc], 2 * kXChunkBytes);
+            tma_load_3d_pair(smem_x + kc * kXChunkBytes, &tmap_x, &sh->x_full[kc], kc * 64, static_cast<int>(rank) * kTile, clip);
+          }
         }
       }
     }
   } else if (warp == kIssueWarp0 + 2) {
     // ------------------------------------------------------------ projection MMAs (leader CTA only)
-    if (leader && lane == 0) {
+    if (leader) {
+      const bool one = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int chunk = 0;                 // running count of K chunks issued
@@ -265,17 +275,20 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
           const uint64_t b_desc = umma_desc_sw128(smem_u32(smem_w + stage * kWStageBytes));
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            tc_mma_ss_pair(tmem_base + kAccCol, a_desc + 2u * ks, b_desc + 2u * ks, idesc_proj, (kc | ks) != 0 ? 1u : 0u);
-          tc_commit_pair(&sh->w_empty[stage], 3);
-          if (h == 7) tc_commit_pair(&sh->x_empty[kc], 3);      // the clip's last use of this x chunk
+            if (one) tc_mma_ss_pair(tmem_base + kAccCol, a_desc + 2u * ks, b_desc + 2u * ks, idesc_proj, (kc | ks) != 0 ? 1u : 0u);
+          if (one) {
+            tc_commit_pair(&sh->w_empty[stage], 3);
+            if (h == 7) tc_commit_pair(&sh->x_empty[kc], 3);      // the clip's last use of this x chunk
+          }
           if (++stage == kWStages) { stage = 0; phase ^= 1u; }
         }
-        tc_commit_pair(&sh->acc_full, 3);
+        if (one) tc_commit_pair(&sh->acc_full, 3);
       }
     }
   } else if (warp == kIssueWarp0 + 3) {
     // ------------------------------------------------------------ attention MMAs (leader CTA only)
-    if (leader && lane == 0) {
+    if (leader) {
+      const bool one = elect_one();
       constexpr uint32_t idesc_s = umma_idesc_f16(2 * kTile, 2 * kTile, 1, 1, 0, 0);                        // bf16 q, k
       constexpr uint32_t idesc_pv = umma_idesc_f16(2 * kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 0);  // V^T is K-major
       const uint64_t k_desc = umma_desc_sw128(smem_u32(smem_k));
@@ -286,9 +299,11 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
         tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks)
-          tc_mma_ts_pair(tmem_base + kSCol, tmem_base + kQCol + 8u * ks, k_desc + 2u * ks, idesc_s, ks != 0 ? 1u : 0u);
-        tc_commit_pair(&sh->s_full, 3);
-        tc_commit_pair(&sh->qk_free, 3);
+          if (one) tc_mma_ts_pair(tmem_base + kSCol, tmem_base + kQCol + 8u * ks, k_desc + 2u * ks, idesc_s, ks != 0 ? 1u : 0u);
+        if (one) {
+          tc_commit_pair(&sh->s_full, 3);
+          tc_commit_pair(&sh->qk_free, 3);
+        }
         const uint64_t v_desc = umma_desc_sw128(smem_u32(smem_vt + (g & 1) * kVtBufBytes));
 #pragma unroll 1
         for (int team = 0; team < 2; ++team) {
@@ -299,11 +314,11 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
           for (int ks = 0; ks < kTile / 16; ++ks) {
             // keys 128 team + 16 ks ..: tile (2 team + ks / 4) of V^T, 32 bytes per 16 keys inside the tile
             const uint64_t b = v_desc + static_cast<uint64_t>((2 * team + (ks >> 2)) * (kVtTileBytes >> 4)) + 2u * (ks & 3);
-            tc_mma_ts_pair(p_addr + kOOff, p_addr + 8u * ks, b, idesc_pv, ks != 0 ? 1u : 0u);
+            if (one) tc_mma_ts_pair(p_addr + kOOff, p_addr + 8u * ks, b, idesc_pv, ks != 0 ? 1u : 0u);
           }
-          tc_commit_pair(&sh->o_full[team], 3);
+          if (one) tc_commit_pair(&sh->o_full[team], 3);
         }
-        tc_commit_pair(&sh->v_free[g & 1], 3);
+        if (one) tc_commit_pair(&sh->v_free[g & 1], 3);
       }
     }
   } else if (warp < kEpiWarps) {

@@ -9,14 +9,17 @@
 // (src/fast_mimi/model.py:1961, :2059).
 //
 // Unlike the QKV projection kernel, which keeps its x tile resident because K is only 512, both operands
-// stream here: a stage holds a 128 x 64 slice of a and a 128 x 64 slice of W per CTA (32 KB), six stages deep.
+// stream here: a stage holds a 128 x 64 slice of a and a 128 x 64 slice of W per CTA (32 KB), five stages deep.
 // Two CTAs form a pair (cluster of 2, tcgen05 cta_group::2): one tcgen05.mma multiplies the pair's 256 rows by
 // 256 weight rows, each CTA contributing half of the weight tile.  Accumulators: two 256-column TMEM buffers
 // per CTA, so the epilogue of one unit overlaps the MMAs of the next.  Persistent: (row-tile pair, 256-wide
 // output tile) units, numbered row-tile-major, are dealt round-robin to the pairs, so the output tiles of a
 // row tile are computed at the same time by neighbouring pairs and share its a slices through L2.
-// Warps 0-7: epilogue (two per TMEM lane group, two 64-column groups each).  Warp 8: TMA producer (+ TMEM
-// allocation).  Warp 9: MMA issuer (leader CTA only).
+// Warps 0-15: epilogue (four per TMEM lane group, one 64-column group of the unit each): with the exact GELU the
+// epilogue, not the tensor core, bounds the K = 512 layers, and eight warps left half of the schedulers' issue slots
+// unused.  Warp 16: TMA producer (+ TMEM allocation).  Warp 17: MMA issuer (leader CTA only).  Five warps per SM
+// sub-partition leave 96 registers per thread at launch; the load / issue warpgroup shrinks to 32 and the epilogue
+// warpgroups grow to 112 (setmaxnreg: 512 x 112 + 128 x 32 = 640 x 96).
 #include <type_traits>
 
 #include "fm_common.cuh"
@@ -29,14 +32,15 @@ constexpr int kBlockM = 128;           // rows per CTA
 constexpr int kBlockN = 256;           // outputs per unit
 constexpr int kHalfN = kBlockN / 2;    // weight rows loaded by each CTA of the pair
 constexpr int kBlockK = 64;            // one 128-byte swizzle row of 16-bit values
-constexpr int kStages = 6;
+constexpr int kStages = 5;
 constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
 constexpr int kBBytes = kHalfN * kBlockK * 2;    // 16 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSlabBytes = 32 * 128;             // one warp's staging: 32 rows x 128 bytes
-constexpr int kEpiWarps = 8;
-constexpr int kGroupsPerWarp = 16 / kEpiWarps;   // a unit has four 64-column groups per lane group
-constexpr int kThreads = (kEpiWarps + 2) * 32;
+constexpr int kEpiWarps = 16;
+constexpr int kThreads = (kEpiWarps + 4) * 32;   // five warpgroups; the last one holds the producer and the issuer
+constexpr int kEpiRegs = 112, kIssueRegs = 32;
+static_assert(kEpiWarps * 32 * kEpiRegs + 128 * kIssueRegs <= kThreads * 96, "register pool of the launch");
 constexpr int kTmemCols = 512;
 constexpr int kSmemBytes = 1024 /*align*/ + kStages * kStageBytes + kEpiWarps * kSlabBytes + 256;
 
@@ -44,7 +48,7 @@ struct Barriers {
   uint64_t full[kStages];      // used in the leader: bytes of both CTAs' a and W slices
   uint64_t empty[kStages];     // per CTA: stage consumed by the tensor core
   uint64_t acc_full[2];        // per CTA: accumulator buffer complete
-  uint64_t acc_empty[2];       // used in the leader: 16 epilogue warps (8 per CTA) drained the buffer
+  uint64_t acc_empty[2];       // used in the leader: 32 epilogue warps (16 per CTA) drained the buffer
   uint32_t tmem_base;
   uint32_t skip;
   CtaCtl ctl;
@@ -136,7 +140,9 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
   if (skip) {
     // a previous kernel already reported a timeout through this status word: do nothing
-  } else if (warp == kEpiWarps) {
+  } else if (warp >= kEpiWarps) {
+   warpgroup_reg_dec<kIssueRegs>();
+   if (warp == kEpiWarps) {
     // ------------------------------------------------------------ TMA producer (one thread per CTA)
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
@@ -157,9 +163,12 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         }
       }
     }
-  } else if (warp == kEpiWarps + 1) {
+   } else if (warp == kEpiWarps + 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (leader && lane == 0) {
+    // The whole warp walks the loop and one elected lane issues (warp-uniform control flow keeps the descriptors in
+    // uniform registers; a single lane under a lane test issues the same sequence a third slower).
+    if (leader) {
+      const bool elected = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       for (int i = 0; i < u_count; ++i) {
@@ -176,18 +185,20 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           const uint64_t b_desc = umma_desc_sw128(base + kABytes);
 #pragma unroll
           for (int ks = 0; ks < kBlockK / 16; ++ks) {
-            tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
+            if (elected) tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
           }
-          tc_commit_pair(&bars->empty[stage], 3);
+          if (elected) tc_commit_pair(&bars->empty[stage], 3);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        tc_commit_pair(&bars->acc_full[buf], 3);
+        if (elected) tc_commit_pair(&bars->acc_full[buf], 3);
       }
     }
+   }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 0..7 of both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 0..15 of both CTAs)
+    warpgroup_reg_inc<kEpiRegs>();
     const int lg = warp & 3;      // TMEM lane group: rows 32*lg .. 32*lg+31 of the tile
-    const int gsel = warp >> 2;   // which two of the unit's four 64-column groups
+    const int g = warp >> 2;      // which of the unit's four 64-column groups
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(&bars->acc_empty[0]), 0);
     uint8_t* slab = smem_out + warp * kSlabBytes;
     for (int i = 0; i < u_count; ++i) {
@@ -200,19 +211,16 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
-#pragma unroll 1
-      for (int g = gsel * kGroupsPerWarp; g < (gsel + 1) * kGroupsPerWarp; ++g) {
+      {
         const int col0 = ntile * kBlockN + g * 64;         // first output channel of this group
         uint32_t raw_lo[32], raw_hi[32];
         tmem_ld32(t_row + g * 64, raw_lo);
         tmem_ld32(t_row + g * 64 + 32, raw_hi);
         tmem_ld_wait();
-        if (g == (gsel + 1) * kGroupsPerWarp - 1) {
-          // Last read of the accumulator by this warp: hand it back before the arithmetic and the stores.
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
-        }
+        // The warp's only read of the accumulator: hand it back before the arithmetic and the stores.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
         float v[64];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {

@@ -101,20 +101,27 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   CtaCtl* ctl = &bars->ctl;
 
   if (warp == 4) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
-      mbar_arrive_expect_tx(&bars->q_full, kTileBytes);
-      tma_load_3d(smem_q, &tmap_q, &bars->q_full, head * kD, q0, clip);
+    // The 32 lanes walk the loop together and one elected lane issues copies, MMAs and commits (warp-uniform
+    // control flow keeps the descriptors in uniform registers; a lone lane under a lane test issues slower).
+    {
+      const bool one = elect_one();
+      if (one) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        mbar_arrive_expect_tx(&bars->q_full, kTileBytes);
+        tma_load_3d(smem_q, &tmap_q, &bars->q_full, head * kD, q0, clip);
+      }
       auto load_kv = [&](int jj) {
         const int st = jj % kKvStages;
         const uint32_t use = static_cast<uint32_t>(jj / kKvStages);
         mbar_wait(&bars->kv_empty[st], (use & 1u) ^ 1u, ctl, status, kErrWaitConsumer);
-        mbar_arrive_expect_tx(&bars->kv_full[st], 2 * kTileBytes);
-        const int k0 = (j_lo + jj) * kTile;
-        tma_load_3d(smem_kv + (2 * st) * kTileBytes, &tmap_k, &bars->kv_full[st], head * kD, k0, clip);
-        tma_load_3d(smem_kv + (2 * st + 1) * kTileBytes, &tmap_v, &bars->kv_full[st], head * kD, k0, clip);
+        if (one) {
+          mbar_arrive_expect_tx(&bars->kv_full[st], 2 * kTileBytes);
+          const int k0 = (j_lo + jj) * kTile;
+          tma_load_3d(smem_kv + (2 * st) * kTileBytes, &tmap_k, &bars->kv_full[st], head * kD, k0, clip);
+          tma_load_3d(smem_kv + (2 * st + 1) * kTileBytes, &tmap_v, &bars->kv_full[st], head * kD, k0, clip);
+        }
       };
       for (int jj = 0; jj < n_kv && jj < kKvStages; ++jj) load_kv(jj);
 
@@ -130,8 +137,8 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const uint64_t k_desc = umma_desc_sw128(smem_u32(smem_kv + (2 * st) * kTileBytes));
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks)
-          tc_mma_ss(tmem_s, q_desc + 2u * ks, k_desc + 2u * ks, idesc_qk, ks != 0 ? 1u : 0u);
-        tc_commit(&bars->s_full);
+          if (one) tc_mma_ss(tmem_s, q_desc + 2u * ks, k_desc + 2u * ks, idesc_qk, ks != 0 ? 1u : 0u);
+        if (one) tc_commit(&bars->s_full);
 
         // P_j is in shared memory once all four softmax warps have arrived.
         mbar_wait(&bars->p_full, static_cast<uint32_t>(jj) & 1u, ctl, status, kErrWaitConsumer);
@@ -146,11 +153,14 @@ band_attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           const uint8_t* p_half = (ks >> 2) == 0 ? smem_kv + (2 * st) * kTileBytes : smem_p_hi;
           const uint64_t p_desc = umma_desc_sw128(smem_u32(p_half)) + 2u * (ks & 3);
           // B = V (MN-major): 16 keys = 16 rows of 128 B = 2048 B per step.
-          tc_mma_ss(tmem_o + ob * kD, p_desc, v_desc + static_cast<uint64_t>(ks) * (2048u >> 4), idesc_pv,
-                    ks != 0 ? 1u : 0u);
+          if (one)
+            tc_mma_ss(tmem_o + ob * kD, p_desc, v_desc + static_cast<uint64_t>(ks) * (2048u >> 4), idesc_pv,
+                      ks != 0 ? 1u : 0u);
         }
-        tc_commit(&bars->o_full[ob]);
-        tc_commit(&bars->kv_empty[st]);
+        if (one) {
+          tc_commit(&bars->o_full[ob]);
+          tc_commit(&bars->kv_empty[st]);
+        }
         if (jj + kKvStages < n_kv) load_kv(jj + kKvStages);
       }
     }

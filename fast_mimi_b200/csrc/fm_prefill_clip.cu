@@ -115,9 +115,12 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
   if (warp >= kSoftmaxWarps) {
     // ------------------------------------------------------------ three single-purpose issuing warps,
-    // each a plain in-order loop with blocking waits (lane 0 only):
+    // each a plain in-order loop with blocking waits.  All 32 lanes walk the loop and one elected lane issues the
+    // copies, MMAs and commits: with warp-uniform control flow the descriptors stay in uniform registers, and a
+    // wait / few MMAs / commit sequence issues a third faster than from a single lane under a lane test.
     //   warp 16: Q/K loads + score products      warp 17: P V products      warp 18: V loads
     const int role = warp - kSoftmaxWarps;
+    const bool one = elect_one();
     constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
     constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
     auto slot_addr = [&](int g) { return tmem_base + static_cast<uint32_t>((g & 3) * kTile); };
@@ -128,14 +131,17 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       const uint64_t v = umma_desc_sw128(smem_u32(v_tile));
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks)
-        tc_mma_ts(slot_addr(g_o) + kOCol, slot_addr(g_p) + kPCol + 8u * ks, v + static_cast<uint64_t>(ks) * 128u, idesc_pv,
+        if (one) tc_mma_ts(slot_addr(g_o) + kOCol, slot_addr(g_p) + kPCol + 8u * ks, v + static_cast<uint64_t>(ks) * 128u, idesc_pv,
                   (accumulate || ks != 0) ? 1u : 0u);
     };
-    if (lane == 0 && role == 0) {
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_q32);
-      tma_prefetch_desc(&tmap_k);
+    if (role == 0) {
+      if (one) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_q32);
+        tma_prefetch_desc(&tmap_k);
+      }
       auto load_qk = [&](int n) {
+        if (!one) return;
         const int item = blockIdx.x + n * gridDim.x;
         const int c = item >> 3, h = item & 7, b = n & 1;
         uint8_t* base = smem + b * kQkBytes;
@@ -164,12 +170,15 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const uint64_t qd = umma_desc_sw128(smem_u32(base + (kind == 0 ? 0 : 1) * kTileBytes));
           const uint64_t kd = umma_desc_sw128(smem_u32(base + (kind == 2 ? 3 : 2) * kTileBytes));
 #pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(slot_addr(g), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
-          tc_commit(&sh->s_full[g & 3]);
-          if (kind == 2) tc_commit(&sh->qk_done[n & 1]);
+          for (int ks = 0; ks < kD / 16; ++ks)
+            if (one) tc_mma_ss(slot_addr(g), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
+          if (one) {
+            tc_commit(&sh->s_full[g & 3]);
+            if (kind == 2) tc_commit(&sh->qk_done[n & 1]);
+          }
         }
       }
-    } else if (lane == 0 && role == 1) {
+    } else if (role == 1) {
       // every job's O = P V goes into its own slot, in job order
       for (int g = 0; g < n_jobs; ++g) {
         const int n = g / 3, kind = g % 3;
@@ -177,11 +186,13 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         mbar_wait(&sh->p_full[g & 3], job_phase(g), ctl, status, kErrWaitConsumer);
         tc_fence_after_sync();
         issue_pv(g, g, smem_v + (n & 1) * kVBytes + (kind == 2 ? kTileBytes : 0), false);
-        tc_commit(&sh->o_full[g & 3]);
-        if (kind == 2) tc_commit(&sh->pv_done[n & 1]);
+        if (one) {
+          tc_commit(&sh->o_full[g & 3]);
+          if (kind == 2) tc_commit(&sh->pv_done[n & 1]);
+        }
       }
-    } else if (lane == 0 && role == 2) {
-      tma_prefetch_desc(&tmap_v);
+    } else if (role == 2) {
+      if (one) tma_prefetch_desc(&tmap_v);
       for (int n = 0; n < n_local; ++n) {
         const int b = n & 1;
         if (n >= 2) {
@@ -192,9 +203,11 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const int item = blockIdx.x + n * gridDim.x;
         const int c = item >> 3, h = item & 7;
         uint8_t* base = smem_v + b * kVBytes;
-        mbar_arrive_expect_tx(&sh->v_full[b], kVBytes);
-        tma_load_3d(base, &tmap_v, &sh->v_full[b], h * kD, 0, c);
-        tma_load_3d(base + kTileBytes, &tmap_v, &sh->v_full[b], h * kD, kTile, c);
+        if (one) {
+          mbar_arrive_expect_tx(&sh->v_full[b], kVBytes);
+          tma_load_3d(base, &tmap_v, &sh->v_full[b], h * kD, 0, c);
+          tma_load_3d(base + kTileBytes, &tmap_v, &sh->v_full[b], h * kD, kTile, c);
+        }
       }
     }
   } else {

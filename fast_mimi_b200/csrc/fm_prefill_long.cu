@@ -144,15 +144,22 @@ band_attn_long_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   auto step_phase = [](int n) { return static_cast<uint32_t>(n >> 1) & 1u; };
 
   if (warp >= kSoftmaxWarps) {
+    // All 32 lanes of an issuing warp walk its loop and one elected lane issues copies, MMAs and commits:
+    // warp-uniform control flow keeps the descriptors in uniform registers and the sequences issue faster than
+    // from a single lane under a lane test.
     const int role = warp - kSoftmaxWarps;
+    const bool one = elect_one();
     constexpr uint32_t idesc_qk = umma_idesc_f16(kTile, kTile, 1, 1, 0, 0);
     constexpr uint32_t idesc_pv = umma_idesc_f16(kTile, kD, Pack16<VT>::kFmt, Pack16<VT>::kFmt, 0, 1);
     auto slot_addr = [&](int g) { return tmem_base + static_cast<uint32_t>((g & 3) * kTile); };
-    if (lane == 0 && role == 0) {
+    if (role == 0) {
       // ---------------------------------------------------------- Q / K loads + score products
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
+      if (one) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+      }
       auto load_qk = [&](const Walk& w) {
+        if (!one) return;
         const int b = w.n & 1;
         const int u_lo = w.first() ? w.first_tile_loaded() : w.t;     // K tiles u_lo .. t arrive with this step
         mbar_arrive_expect_tx(&sh->qk_full[b], static_cast<uint32_t>((w.t - u_lo + 2) * kTileBytes));
@@ -189,10 +196,13 @@ band_attn_long_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           if (u >= 0) {
             const uint64_t kd = umma_desc_sw128(smem_u32(smem_k + (u & 3) * kTileBytes));
 #pragma unroll
-            for (int ks = 0; ks < kD / 16; ++ks) tc_mma_ss(slot_addr(g), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
+            for (int ks = 0; ks < kD / 16; ++ks)
+              if (one) tc_mma_ss(slot_addr(g), qd + 2u * ks, kd + 2u * ks, idesc_qk, ks != 0);
           }
-          tc_commit(&sh->s_full[g & 3]);
-          if (kind == 2) tc_commit(&sh->qk_done[n & 1]);
+          if (one) {
+            tc_commit(&sh->s_full[g & 3]);
+            if (kind == 2) tc_commit(&sh->qk_done[n & 1]);
+          }
         }
         if (nxt.valid() && nxt.first()) {
           // A new run: its tiles go into ring slots that this step's tiles may still occupy.
@@ -200,7 +210,7 @@ band_attn_long_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           load_qk(nxt);
         }
       }
-    } else if (lane == 0 && role == 1) {
+    } else if (role == 1) {
       // ---------------------------------------------------------- P V products
       for (Walk w(n_runs, n_seg, seg_tiles, n_tiles); w.valid(); w.next()) {
         const int n = w.n;
@@ -216,18 +226,21 @@ band_attn_long_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           const uint64_t v = umma_desc_sw128(smem_u32(smem_v + (u & 3) * kTileBytes));
 #pragma unroll
           for (int ks = 0; ks < kTile / 16; ++ks)
-            tc_mma_ts(slot_addr(3 * n + 2) + kOCol, slot_addr(3 * n + kind) + kPCol + 8u * ks,
-                      v + static_cast<uint64_t>(ks) * 128u, idesc_pv, (accumulate || ks != 0) ? 1u : 0u);
+            if (one)
+              tc_mma_ts(slot_addr(3 * n + 2) + kOCol, slot_addr(3 * n + kind) + kPCol + 8u * ks,
+                        v + static_cast<uint64_t>(ks) * 128u, idesc_pv, (accumulate || ks != 0) ? 1u : 0u);
           accumulate = true;
         }
-        tc_commit(&sh->o_full[(3 * n + 2) & 3]);
-        tc_commit(&sh->o_full[(3 * n + 1) & 3]);   // nobody waits on these two; one completion per slot use
-        tc_commit(&sh->o_full[(3 * n) & 3]);
-        tc_commit(&sh->pv_done[n & 1]);
+        if (one) {
+          tc_commit(&sh->o_full[(3 * n + 2) & 3]);
+          tc_commit(&sh->o_full[(3 * n + 1) & 3]);   // nobody waits on these two; one completion per slot use
+          tc_commit(&sh->o_full[(3 * n) & 3]);
+          tc_commit(&sh->pv_done[n & 1]);
+        }
       }
-    } else if (lane == 0 && role == 2) {
+    } else if (role == 2) {
       // ---------------------------------------------------------- V loads
-      tma_prefetch_desc(&tmap_v);
+      if (one) tma_prefetch_desc(&tmap_v);
       for (Walk w(n_runs, n_seg, seg_tiles, n_tiles); w.valid(); w.next()) {
         const int n = w.n, b = n & 1;
         int u_lo = w.t;
@@ -239,9 +252,11 @@ band_attn_long_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           // the slot held tile t-4, last read by step n-2 of this run
           mbar_wait(&sh->pv_done[b], step_phase(n - 2), ctl, status, kErrWaitMma);
         }
-        mbar_arrive_expect_tx(&sh->v_full[b], static_cast<uint32_t>((w.t - u_lo + 1) * kTileBytes));
-        for (int u = u_lo; u <= w.t; ++u)
-          tma_load_3d(smem_v + (u & 3) * kTileBytes, &tmap_v, &sh->v_full[b], w.head() * kD, u * kTile, w.clip());
+        if (one) {
+          mbar_arrive_expect_tx(&sh->v_full[b], static_cast<uint32_t>((w.t - u_lo + 1) * kTileBytes));
+          for (int u = u_lo; u <= w.t; ++u)
+            tma_load_3d(smem_v + (u & 3) * kTileBytes, &tmap_v, &sh->v_full[b], w.head() * kD, u * kTile, w.clip());
+        }
       }
     }
   } else {

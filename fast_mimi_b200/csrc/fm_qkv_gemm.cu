@@ -152,7 +152,11 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
     }
   } else if (warp == kEpiWarps + 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (leader && lane == 0) {
+    // The whole warp walks the loop and one elected lane issues: with warp-uniform control flow the descriptors
+    // stay in uniform registers, and the per-chunk wait / four MMAs / commit sequence keeps the tensor core fed
+    // (128 cycles per MMA in isolation against 195 when a single lane runs the same loop under a lane test).
+    if (leader) {
+      const bool elected = elect_one();
       int stage = 0, gen = -1, cur_tile = -1;
       uint32_t phase = 0;
       for (int i = 0; i < u_count; ++i) {
@@ -175,13 +179,15 @@ qkv_rope_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 #pragma unroll
           for (int ks = 0; ks < kBlockK / 16; ++ks) {
             // +32 bytes per 16-element K step inside the 128-byte swizzle row (encoded >> 4).
-            tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
+            if (elected) tc_mma_ss_pair(d_tmem, a_desc + 2u * ks, b_desc + 2u * ks, idesc, (kc | ks) != 0 ? 1u : 0u);
           }
-          tc_commit_pair(&bars->b_empty[stage], 3);     // frees the stage in both CTAs
-          if (roll) tc_commit_pair(&bars->a_empty[kc], 3);   // and, on a tile's last unit, the x chunk
+          if (elected) {
+            tc_commit_pair(&bars->b_empty[stage], 3);     // frees the stage in both CTAs
+            if (roll) tc_commit_pair(&bars->a_empty[kc], 3);   // and, on a tile's last unit, the x chunk
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        tc_commit_pair(&bars->acc_full[buf], 3);        // both CTAs' epilogues may read their TMEM
+        if (elected) tc_commit_pair(&bars->acc_full[buf], 3);        // both CTAs' epilogues may read their TMEM
       }
     }
   } else {
