@@ -9,17 +9,21 @@
 // (src/fast_mimi/model.py:1961, :2059).
 //
 // Unlike the QKV projection kernel, which keeps its x tile resident because K is only 512, both operands
-// stream here: a stage holds a 128 x 64 slice of a and a 128 x 64 slice of W per CTA (32 KB), five stages deep.
+// stream here: a stage holds a 128 x 64 slice of a and a 128 x 64 slice of W per CTA (32 KB), five or six stages deep.
 // Two CTAs form a pair (cluster of 2, tcgen05 cta_group::2): one tcgen05.mma multiplies the pair's 256 rows by
 // 256 weight rows, each CTA contributing half of the weight tile.  Accumulators: two 256-column TMEM buffers
 // per CTA, so the epilogue of one unit overlaps the MMAs of the next.  Persistent: (row-tile pair, 256-wide
 // output tile) units, numbered row-tile-major, are dealt round-robin to the pairs, so the output tiles of a
 // row tile are computed at the same time by neighbouring pairs and share its a slices through L2.
-// Warps 0-15: epilogue (four per TMEM lane group, one 64-column group of the unit each): with the exact GELU the
-// epilogue, not the tensor core, bounds the K = 512 layers, and eight warps left half of the schedulers' issue slots
-// unused.  Warp 16: TMA producer (+ TMEM allocation).  Warp 17: MMA issuer (leader CTA only).  Five warps per SM
-// sub-partition leave 96 registers per thread at launch; the load / issue warpgroup shrinks to 32 and the epilogue
-// warpgroups grow to 112 (setmaxnreg: 512 x 112 + 128 x 32 = 640 x 96).
+// Two shapes of the same kernel (template parameter kWide):
+//   wide    warps 0-15 epilogue (four per TMEM lane group, one 64-column group of the unit each), warp 16 TMA
+//           producer (+ TMEM allocation), warp 17 MMA issuer (leader CTA only); five stages.  For epilogues that
+//           carry arithmetic (the exact GELU, the candidate records of the quantiser search): there the epilogue,
+//           not the tensor core, bounds the kernel, and eight warps cannot hide its latencies.  Five warps per SM
+//           sub-partition leave 96 registers per thread at launch; the load / issue warpgroup shrinks to 32 and the
+//           epilogue warpgroups grow to 112 (setmaxnreg: 512 x 112 + 128 x 32 = 640 x 96).
+//   narrow  warps 0-7 epilogue (two 64-column groups each), warps 8 and 9 producer and issuer; six stages (the
+//           shared memory of eight staging slabs buys the sixth, which the K = 2048 layer uses).
 #include <type_traits>
 
 #include "fm_common.cuh"
@@ -32,23 +36,27 @@ constexpr int kBlockM = 128;           // rows per CTA
 constexpr int kBlockN = 256;           // outputs per unit
 constexpr int kHalfN = kBlockN / 2;    // weight rows loaded by each CTA of the pair
 constexpr int kBlockK = 64;            // one 128-byte swizzle row of 16-bit values
-constexpr int kStages = 5;
 constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
 constexpr int kBBytes = kHalfN * kBlockK * 2;    // 16 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSlabBytes = 32 * 128;             // one warp's staging: 32 rows x 128 bytes
-constexpr int kEpiWarps = 16;
-constexpr int kThreads = (kEpiWarps + 4) * 32;   // five warpgroups; the last one holds the producer and the issuer
+template <bool kWide> struct Shape {
+  static constexpr int kStages = kWide ? 5 : 6;
+  static constexpr int kEpiWarps = kWide ? 16 : 8;
+  static constexpr int kGroupsPerWarp = 16 / kEpiWarps;   // a unit has four 64-column groups per lane group
+  // wide: five warpgroups, the last one holds the producer and the issuer; narrow: epilogue warps + 2
+  static constexpr int kThreads = kWide ? (kEpiWarps + 4) * 32 : (kEpiWarps + 2) * 32;
+  static constexpr int kSmemBytes = 1024 /*align*/ + kStages * kStageBytes + kEpiWarps * kSlabBytes + 256;
+};
 constexpr int kEpiRegs = 112, kIssueRegs = 32;
-static_assert(kEpiWarps * 32 * kEpiRegs + 128 * kIssueRegs <= kThreads * 96, "register pool of the launch");
+static_assert(512 * kEpiRegs + 128 * kIssueRegs <= Shape<true>::kThreads * 96, "register pool of the launch");
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = 1024 /*align*/ + kStages * kStageBytes + kEpiWarps * kSlabBytes + 256;
 
 struct Barriers {
-  uint64_t full[kStages];      // used in the leader: bytes of both CTAs' a and W slices
-  uint64_t empty[kStages];     // per CTA: stage consumed by the tensor core
+  uint64_t full[6];            // used in the leader: bytes of both CTAs' a and W slices
+  uint64_t empty[6];           // per CTA: stage consumed by the tensor core
   uint64_t acc_full[2];        // per CTA: accumulator buffer complete
-  uint64_t acc_empty[2];       // used in the leader: 32 epilogue warps (16 per CTA) drained the buffer
+  uint64_t acc_empty[2];       // used in the leader: the epilogue warps of both CTAs drained the buffer
   uint32_t tmem_base;
   uint32_t skip;
   CtaCtl ctl;
@@ -88,12 +96,14 @@ struct LinearArgs {
 // kOut: 0 = BF16, 1 = FP16, 2 = FP32 (type of y and of the residual); 3 = no y at all: the products are the inner
 // products x . e_j of a nearest-entry search and the epilogue reduces every 64 of them to one 16-byte record
 // {min_j d_j, 64-bit mask of the entries with d_j <= min + margin[row]},  d_j = |e_j|^2 - 2 x . e_j  (see fm_rvq.cu).
-template <int kOut>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(lin::kThreads, 1)
+template <int kOut, bool kWide>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(lin::Shape<kWide>::kThreads, 1)
 linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_y, LinearArgs args, int total_units, uint32_t idesc,
                    int* status) {
   using namespace lin;
+  constexpr int kStages = Shape<kWide>::kStages, kEpiWarps = Shape<kWide>::kEpiWarps;
+  constexpr int kGroupsPerWarp = Shape<kWide>::kGroupsPerWarp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_stage = smem;                                  // kStages x [a slice | W slice]
@@ -141,7 +151,7 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   if (skip) {
     // a previous kernel already reported a timeout through this status word: do nothing
   } else if (warp >= kEpiWarps) {
-   warpgroup_reg_dec<kIssueRegs>();
+   if constexpr (kWide) warpgroup_reg_dec<kIssueRegs>();
    if (warp == kEpiWarps) {
     // ------------------------------------------------------------ TMA producer (one thread per CTA)
     if (lane == 0) {
@@ -196,9 +206,9 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
    }
   } else {
     // ------------------------------------------------------------ epilogue (warps 0..15 of both CTAs)
-    warpgroup_reg_inc<kEpiRegs>();
+    if constexpr (kWide) warpgroup_reg_inc<kEpiRegs>();
     const int lg = warp & 3;      // TMEM lane group: rows 32*lg .. 32*lg+31 of the tile
-    const int g = warp >> 2;      // which of the unit's four 64-column groups
+    const int gsel = warp >> 2;   // which of the unit's four 64-column groups (wide), or which two (narrow)
     const uint32_t acc_empty_leader = map_to_cta(smem_u32(&bars->acc_empty[0]), 0);
     uint8_t* slab = smem_out + warp * kSlabBytes;
     for (int i = 0; i < u_count; ++i) {
@@ -211,16 +221,19 @@ linear_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       mbar_wait(&bars->acc_full[buf], use & 1u, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lg * 32) << 16) + static_cast<uint32_t>(buf * kBlockN);
-      {
+#pragma unroll 1
+      for (int g = gsel * kGroupsPerWarp; g < (gsel + 1) * kGroupsPerWarp; ++g) {
         const int col0 = ntile * kBlockN + g * 64;         // first output channel of this group
         uint32_t raw_lo[32], raw_hi[32];
         tmem_ld32(t_row + g * 64, raw_lo);
         tmem_ld32(t_row + g * 64 + 32, raw_hi);
         tmem_ld_wait();
-        // The warp's only read of the accumulator: hand it back before the arithmetic and the stores.
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+        if (g == (gsel + 1) * kGroupsPerWarp - 1) {
+          // Last read of the accumulator by this warp: hand it back before the arithmetic and the stores.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster_relaxed(acc_empty_leader + static_cast<uint32_t>(buf) * 8u);
+        }
         float v[64];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -380,11 +393,20 @@ int launch_linear_gemm(const void* a, const void* w, void* y, const float* scale
   const int fmt = in_dtype == 1 ? 0 : 1;   // tcgen05 kind::f16 operand format: 0 = F16, 1 = BF16
   const uint32_t idesc = umma_idesc_f16(2 * kBlockM, kBlockN, fmt, fmt, 0, 0);
   LinearArgs args = {scale, resid, M, N, K, gelu ? 1 : 0, out_dtype == 3 ? static_cast<uint4*>(y) : nullptr};
-  auto kern = out_dtype == 3 ? linear_gemm_kernel<3>
-                             : (out_dtype == 2 ? linear_gemm_kernel<2> : (out_dtype == 1 ? linear_gemm_kernel<1> : linear_gemm_kernel<0>));
-  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes);
+  // The wide shape where the epilogue carries arithmetic (GELU, candidate records), the narrow one otherwise.
+  const bool wide = gelu || out_dtype == 3;
+  using Kern = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, LinearArgs, int, uint32_t, int*);
+  Kern kern;
+  if (wide)
+    kern = out_dtype == 3 ? linear_gemm_kernel<3, true>
+                          : (out_dtype == 2 ? linear_gemm_kernel<2, true> : (out_dtype == 1 ? linear_gemm_kernel<1, true> : linear_gemm_kernel<0, true>));
+  else
+    kern = out_dtype == 2 ? linear_gemm_kernel<2, false> : (out_dtype == 1 ? linear_gemm_kernel<1, false> : linear_gemm_kernel<0, false>);
+  const int smem_bytes = wide ? Shape<true>::kSmemBytes : Shape<false>::kSmemBytes;
+  const int threads = wide ? Shape<true>::kThreads : Shape<false>::kThreads;
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes);
   if (rc != 0) return rc;
-  kern<<<2 * n_pairs, kThreads, kSmemBytes, st>>>(tmap_a, tmap_w, tmap_y, args, total_units, idesc, status);
+  kern<<<2 * n_pairs, threads, smem_bytes, st>>>(tmap_a, tmap_w, tmap_y, args, total_units, idesc, status);
   return static_cast<int>(cudaGetLastError());
 }
 
