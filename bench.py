@@ -46,7 +46,8 @@ QKV_FLOP_PER_FRAME = 2 * 512 * 1536
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel.  ncu cannot run inside this
 # script, so these come from the captures summarised under profiles/ (same kernels, a 256-clip case: traffic grows in
 # proportion to the clips) scaled by 2 to this workload's 512 clips; the line says so in `traffic_source`.
-NCU_TRAFFIC_BYTES_256_CLIPS = {"qkv_rope_gemm_kernel": 217.5e6, "band_attn_clip_kernel": 237.0e6}
+NCU_TRAFFIC_BYTES_256_CLIPS = {"qkv_rope_gemm_kernel": 217.1e6, "band_attn_clip_kernel": 236.3e6,
+                               "attn_fused_clip_kernel": 85.4e6}
 DTYPE = "bf16 x, W, q, k / fp16 v, p, out / fp32 accumulate"
 
 
@@ -216,7 +217,9 @@ def config_dict() -> dict:
     return {"workload": "batched prefill (benchmark config 3): QKV projection + RoPE + banded causal attention, "
                         "16 layers", "clips_per_gpu": CLIPS, "frames": FRAMES, "layers": LAYERS, "window": WINDOW,
             "heads": 8, "head_dim": 64,
-            "l2": "inputs larger than L2: x and out of one layer are 262 MB (the two-kernel path adds 393 MB of q, k, v)"}
+            "l2": "inputs larger than L2: x and out of one layer call are 262 MB, and all 16 calls of a step read the "
+                  "same x with different weights and write the same out",
+            "kernel": "one launch per layer call: projection + RoPE + banded attention (q, k, v never in memory)"}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -285,22 +288,17 @@ def run_ours(args) -> None:
     stream = torch.cuda.current_stream()
 
     def step(events=None, xin=None, outbuf=None, clips=CLIPS):
-        """One pass of the 16 layers: projection + RoPE kernel, then the whole-clip attention kernel (what the public
-        entry point for a cache-free call, ops.attention_prefill, runs; issued as its two halves here so that each
-        kernel can be timed with events on the launching stream)."""
+        """One pass of the 16 layers through the public entry point for a cache-free call, ops.attention_prefill
+        (for 250-frame clips: one kernel per layer call, projection + RoPE + banded attention)."""
         xin = x if xin is None else xin
         outbuf = out if outbuf is None else outbuf
-        ws_ = (q[:clips], k[:clips], v[:clips])
         for l in range(LAYERS):
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True); e0.record(stream)
-            ops.qkv_rope(xin[:clips], ws[l], cos, sin, out=ws_, status=status)
+            ops.attention_prefill(xin[:clips], ws[l], cos, sin, window=WINDOW, scale=0.125, out=outbuf[:clips], status=status)
             if events is not None:
                 e1 = torch.cuda.Event(enable_timing=True); e1.record(stream)
-            ops.band_attention_prefill(*ws_, window=WINDOW, scale=0.125, out=outbuf[:clips], status=status)
-            if events is not None:
-                e2 = torch.cuda.Event(enable_timing=True); e2.record(stream)
-                events.append((e0, e1, e2))
+                events.append((e0, e1))
 
     # ---- device-resident throughput ---------------------------------------------------------
     for _ in range(args.warmup):
@@ -316,8 +314,7 @@ def run_ours(args) -> None:
         barrier()
     ms_total = start.elapsed_time(stop)
     ops.check_status(status=status)
-    gemm_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in events)
-    attn_ms = statistics.mean(b.elapsed_time(c) for _, b, c in events)
+    fused_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
 
     # ---- parity of the timed configuration's own output -------------------------------------
     # The buffers of the timed run, full-size launches: every layer's result for the first clips against the CPU
@@ -329,33 +326,37 @@ def run_ours(args) -> None:
         xs_cpu = x[:n_par].float().cpu()
         cos_c, sin_c = O.rope_tables(torch.arange(FRAMES))
         worst = 0.0
-        worst_fused = 0.0
-        out_f = torch.empty_like(out)
+        worst_two = 0.0
+        out_2 = torch.empty_like(out)
         for l in range(LAYERS):
-            ops.attention_prefill(x, ws[l], cos, sin, window=WINDOW, scale=0.125, workspace=(q, k, v), out=out, status=status)
-            ops.attention_fused(x, ws[l], cos, sin, window=WINDOW, scale=0.125, out=out_f, status=status)
+            ops.attention_prefill(x, ws[l], cos, sin, window=WINDOW, scale=0.125, out=out, status=status)
+            ops.qkv_rope(x, ws[l], cos, sin, out=(q, k, v), status=status)
+            ops.band_attention_prefill(q, k, v, window=WINDOW, scale=0.125, out=out_2, status=status)
             got = out[:n_par].float().cpu()
             qc, kc, vc = O.qkv_project(xs_cpu, *ws[l].float().cpu().chunk(3, 0))
             qc, kc = O.apply_rope(qc, kc, cos_c, sin_c)
             want = O.band_attention(qc, kc, vc).transpose(1, 2).reshape(n_par, FRAMES, HIDDEN)
             worst = max(worst, O.rel_l2(got, want))
-            worst_fused = max(worst_fused, O.rel_l2(out_f[:n_par].float().cpu(), want))
-        del out_f
+            worst_two = max(worst_two, O.rel_l2(out_2[:n_par].float().cpu(), want))
+        del out_2
         parity = {"rel_l2_max": worst, "clips": n_par, "layers": LAYERS, "tolerance": 2e-3, "ok": worst <= 2e-3,
-                  "rel_l2_max_fused_kernel": worst_fused,
+                  "rel_l2_max_two_kernel_form": worst_two,
                   "what": "output of the full-size launches of the timed configuration vs the CPU oracle"}
 
-    # ---- the same layer as ONE kernel (projection + RoPE + attention, q / k / v never in memory); not in the step ----
-    fused_events: list = []
+    # ---- the same layer call as two kernels (projection + RoPE, then attention, q / k / v through HBM); not in the step ----
+    two_events: list = []
     for it in range(3 + 8):
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True); e2 = torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        ops.attention_fused(x, ws[it % LAYERS], cos, sin, window=WINDOW, scale=0.125, out=out, status=status)
+        ops.qkv_rope(x, ws[it % LAYERS], cos, sin, out=(q, k, v), status=status)
         e1.record(stream)
+        ops.band_attention_prefill(q, k, v, window=WINDOW, scale=0.125, out=out, status=status)
+        e2.record(stream)
         if it >= 3:
-            fused_events.append((e0, e1))
+            two_events.append((e0, e1, e2))
     torch.cuda.synchronize()
-    fused_ms = statistics.mean(a.elapsed_time(b) for a, b in fused_events)
+    gemm_ms = statistics.mean(a.elapsed_time(b) for a, b, _ in two_events)
+    attn_ms = statistics.mean(b.elapsed_time(c) for _, b, c in two_events)
 
     # ---- end to end: pinned host input -> device -> 16 layers -> host --------------------------
     # Every step copies its batch in from pinned memory and its result out; the copies of neighbouring
@@ -475,22 +476,23 @@ def run_ours(args) -> None:
         return None if t is None else 2 * t
 
     kernels = [
-        {"kernel": "qkv_rope_gemm_kernel", "in_step": True, "ms": gemm_ms, "share": gemm_ms / (gemm_ms + attn_ms),
-         "bound": "tensor", "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-         "frac": gemm_tf / peaks["bf16_tflops"], "frac_sustained": gemm_tf / peaks["bf16_tflops_sustained"],
-         "algorithmic_flop": gemm_flop},
-        {"kernel": "band_attn_clip_kernel", "in_step": True, "ms": attn_ms, "share": attn_ms / (gemm_ms + attn_ms),
-         "bound": "hbm", "achieved": attn_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn_gbs / peaks["hbm_gbs"],
-         "frac_sustained": attn_gbs / peaks["hbm_gbs"], "tensor_tflops": attn_flop / (attn_ms / 1e3) / 1e12,
-         "algorithmic_bytes": attn_bytes},
-        {"kernel": "attn_fused_clip_kernel", "in_step": False, "ms": fused_ms, "bound": "tensor",
+        {"kernel": "attn_fused_clip_kernel", "in_step": True, "ms": fused_ms, "share": 1.0, "bound": "tensor",
          "achieved": fused_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fused_tf / peaks["bf16_tflops"],
          "frac_sustained": fused_tf / peaks["bf16_tflops_sustained"],
          "gbs": fused_bytes / (fused_ms / 1e3) / 1e9, "algorithmic_flop": gemm_flop + attn_flop, "algorithmic_bytes": fused_bytes,
-         "note": "one kernel for the whole layer call (x in, attention out, 2.5x fewer HBM bytes); timed after the step, "
-                 "not part of it: the two kernels above are the faster way today"},
+         "note": "the whole layer call in one kernel: x in, attention out (893 FLOP per HBM byte: tensor-bound)"},
+        {"kernel": "qkv_rope_gemm_kernel", "in_step": False, "ms": gemm_ms,
+         "bound": "tensor", "achieved": gemm_tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+         "frac": gemm_tf / peaks["bf16_tflops"], "frac_sustained": gemm_tf / peaks["bf16_tflops_sustained"],
+         "algorithmic_flop": gemm_flop,
+         "note": "first half of the two-kernel form of the same call (other clip lengths, cached calls); timed after the step"},
+        {"kernel": "band_attn_clip_kernel", "in_step": False, "ms": attn_ms,
+         "bound": "hbm", "achieved": attn_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": attn_gbs / peaks["hbm_gbs"],
+         "frac_sustained": attn_gbs / peaks["hbm_gbs"], "tensor_tflops": attn_flop / (attn_ms / 1e3) / 1e12,
+         "algorithmic_bytes": attn_bytes,
+         "note": "second half of the two-kernel form; timed after the step"},
     ]
-    top = max(kernels[:2], key=lambda d: d["ms"])
+    top = kernels[0]
     roofline = {"bound": top["bound"], "achieved": top["achieved"], "peak": top["peak"], "unit": top["unit"],
                 "frac": top["frac"], "frac_sustained": top["frac_sustained"], "traffic": traffic(top["kernel"]),
                 "traffic_source": "profiles/ (ncu capture of a 256-clip launch, scaled x2 by the clips processed)",
@@ -506,7 +508,7 @@ def run_ours(args) -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": config_dict(),
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * LAYERS * 2, "roofline": roofline, "kernels": kernels, "parity": parity,
+            "gpu_launches": args.steps * LAYERS, "roofline": roofline, "kernels": kernels, "parity": parity,
             "host_copy": {"ms_per_step": ms_copy, "gbs_per_gpu": (h2d + d2h) / (ms_copy / 1e3) / 1e9,
                           "gbs_all_gpus": world * (h2d + d2h) / (ms_copy / 1e3) / 1e9,
                           "what": "the e2e loop's pinned-host copies alone (no kernels), all ranks at once, max over ranks: "
@@ -641,8 +643,11 @@ def profile_case(which: str) -> None:
     if which == "prefill":
         x = torch.randn(256, FRAMES, HIDDEN, device=dev, generator=g).bfloat16()
         cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)
+        # the two-kernel form of the call (projection + RoPE, then whole-clip attention), q / k / v through HBM
+        qkv = (torch.empty_like(x), torch.empty_like(x), torch.empty(x.shape, dtype=torch.float16, device=dev))
         for _ in range(4):
-            ops.attention_prefill(x, w, cos, sin)
+            ops.qkv_rope(x, w, cos, sin, out=qkv)
+            ops.band_attention_prefill(*qkv, window=WINDOW)
     elif which == "fused":
         x = torch.randn(256, FRAMES, HIDDEN, device=dev, generator=g).bfloat16()
         cos = torch.ones(1, FRAMES, 64, device=dev); sin = torch.zeros(1, FRAMES, 64, device=dev)

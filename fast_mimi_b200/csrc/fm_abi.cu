@@ -102,9 +102,11 @@ static int prefill_two_kernels(const void* x, const void* w_qkv, const float* co
 int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
                               long long cos_bstride, void* q_ws, void* k_ws, void* v_ws, void* out, int B, int T,
                               int window, float scale, int value_dtype, int* status, void* stream) {
-  // The projection kernel followed by the attention kernel that fits the clip length.  (For clips of 129 .. 256
-  // frames fm_attention_fused_bf16 computes the same in one kernel without the q / k / v round trip; measured on
-  // B200 the pair of kernels is still the faster of the two, so it stays the default.)
+  // Whole clips of 129 .. 256 frames take the one-kernel form (projection + RoPE + attention, q / k / v never in
+  // memory; the workspaces are not touched and may be null); every other length the projection kernel followed by
+  // the attention kernel that fits it.
+  if (T > 128 && T <= 256 && B > 0)
+    return fm_attention_fused_bf16(x, w_qkv, cos, sin, cos_bstride, out, B, T, window, scale, value_dtype, status, stream);
   return prefill_two_kernels(x, w_qkv, cos, sin, cos_bstride, q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype,
                              status, stream);
 }

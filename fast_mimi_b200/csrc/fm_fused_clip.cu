@@ -25,7 +25,8 @@
 //                32s .. 32s+31 for all keys, which is why V is stored split by dimension.
 //   output       normalised in registers and written straight to global memory (128 contiguous bytes per frame-head).
 //
-// TMEM columns per CTA: [0,192) projection accumulator, [192,224) Q, [256,512) scores (P and O overlay them).
+// TMEM columns per CTA: [0,192) projection accumulator, [192,224) Q, [224,228) the teams' row maxima and sums,
+// [256,512) scores (P and O overlay them).
 // Warps: 0-7 epilogue, 8-11 team A, 12-15 team B, 16 W loads (+ TMEM allocation), 17 x loads, 18 projection MMAs
 // (leader CTA), 19 attention MMAs (leader CTA).  Every barrier that gates a pair MMA lives in the leader and
 // counts arrivals from both CTAs; completions are multicast to both.  No TMA multicast anywhere.
@@ -53,7 +54,7 @@ constexpr int kTeamWarp0 = kEpiWarps;             // team A: warps 8-11, team B:
 constexpr int kIssueWarp0 = kEpiWarps + 8;        // W loads, x loads, projection MMAs, attention MMAs
 constexpr int kThreads = (kIssueWarp0 + 4) * 32;
 constexpr int kTmemCols = 512;
-constexpr uint32_t kAccCol = 0, kQCol = 192, kSCol = 256;
+constexpr uint32_t kAccCol = 0, kQCol = 192, kXCol = 224, kSCol = 256;   // kXCol: four columns for the teams' row maxima and sums
 constexpr uint32_t kOOff = 64;                    // inside a team's 128 score columns: P at +0, O at +64
 
 struct Shared {
@@ -69,12 +70,11 @@ struct Shared {
   uint64_t s_full;              // per CTA: scores are in tensor memory
   uint64_t p_full[2];           // leader: team A of both CTAs (8 warps) / team B of CTA 1 (4 warps) wrote P
   uint64_t o_full[2];           // per CTA: O_A / O_B complete
-  uint64_t slot_free;           // leader: the 8 warps that read O are done with the score columns
-  uint64_t xl_full;             // CTA 1: team A published its row maxima and sums
+  uint64_t slot_free;           // leader: the 12 warps that read O (team A of CTA 0, both teams of CTA 1) are done with the score columns
+  uint64_t xl_full;             // CTA 1: both teams (8 warps) published their row maxima and sums
   uint32_t tmem_base;
   uint32_t skip;
   CtaCtl ctl;
-  float xs[kTile][2];           // CTA 1: scaled row maximum (-inf: nothing visible) and row sum of team A
 };
 constexpr int kSharedBytes = static_cast<int>((sizeof(Shared) + 127) & ~size_t(127));
 constexpr int kSmemBytes = 1024 + kKChunks * kXChunkBytes + kWStages * kWStageBytes + kKParkBytes + 2 * kVtBufBytes + kSharedBytes;
@@ -119,11 +119,11 @@ __device__ __forceinline__ void pack_output_row(uint32_t o_addr, float inv, uint
       w[d0 / 2 + j] = Pack16<VT>::pack(__uint_as_float(o[2 * j]) * inv, __uint_as_float(o[2 * j + 1]) * inv);
   }
 }
-// Same for the weighted sum of two partial outputs:  c_a * O_a + c_b * O_b.
+// Half of a row (32 output values) as the weighted sum of two partial outputs, 16 packed words.
 template <typename VT>
-__device__ __forceinline__ void pack_output_row2(uint32_t oa_addr, uint32_t ob_addr, float c_a, float c_b, uint32_t (&w)[32]) {
+__device__ __forceinline__ void pack_output_half2(uint32_t oa_addr, uint32_t ob_addr, float c_a, float c_b, uint32_t (&w)[16]) {
 #pragma unroll
-  for (int d0 = 0; d0 < kD; d0 += 16) {       // 16 columns of each at a time: the 32 packed words stay live throughout
+  for (int d0 = 0; d0 < 32; d0 += 16) {
     uint32_t oa[16], ob[16];
     tmem_ld16(oa_addr + d0, oa);
     tmem_ld16(ob_addr + d0, ob);
@@ -180,8 +180,8 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     mbar_init(&sh->p_full[1], 4);
     mbar_init(&sh->o_full[0], 1);
     mbar_init(&sh->o_full[1], 1);
-    mbar_init(&sh->slot_free, 8);
-    mbar_init(&sh->xl_full, 4);
+    mbar_init(&sh->slot_free, 12);
+    mbar_init(&sh->xl_full, 8);
     sh->ctl.abort = 0;
     sh->skip = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1u : 0u;
     fence_mbar_init();
@@ -427,7 +427,6 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     // ------------------------------------------------------------ softmax teams (team B only where rows see keys >= 128)
     const int team = (warp - kTeamWarp0) >> 2;  // 0: keys 0-127, 1: keys 128-255
     const int lg = warp & 3;
-    const int row = lg * 32 + lane;
     const int w_row0 = static_cast<int>(rank) * kTile + lg * 32;
     const int i = w_row0 + lane;                // this thread's frame
     const uint32_t lane_sel = static_cast<uint32_t>(lg * 32) << 16;
@@ -435,8 +434,12 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
     const uint32_t sa_addr = tmem_base + lane_sel + kSCol;      // team A's columns (CTA 1's team B reads O_A there)
     const uint32_t p_full_l = map_to_cta(smem_u32(&sh->p_full[team]), 0);
     const GroupVis vis(i, w_row0, team * kTile, window);
-    const bool publishes = !leader && team == 0;    // rows 128-255, keys 0-127: a partial result
-    const bool combines = !leader && team == 1;
+    // Rows 128-255 (CTA 1) have two partial results, team A's over keys 0-127 and team B's over keys 128-255.  The
+    // teams exchange their row maxima and sums through four spare tensor-memory columns and each finishes HALF of
+    // every row (team A output dimensions 0-31, team B 32-63), so the combine and the global stores, which sit
+    // between one head's P V product and the next head's scores, are shared by eight warps instead of four.
+    const bool two_parts = !leader;
+    const uint32_t x_addr = tmem_base + lane_sel + kXCol;
     for (int g = 0; g < n_heads_total; ++g) {
       const uint32_t ph = static_cast<uint32_t>(g) & 1u;
       mbar_wait(&sh->s_full, ph, ctl, status, kErrWaitMma);
@@ -444,46 +447,59 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       const float m_raw = tile_row_max(s_addr, vis);
       const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
       const float l_row = tile_row_probs<VT>(s_addr, s_addr, vis, scale_log2e, m_use);
-      if (publishes) {
-        sh->xs[row][0] = (m_raw == -INFINITY) ? -INFINITY : m_use;
-        sh->xs[row][1] = l_row;
+      if (two_parts) {
+        // scaled row maximum (-inf: nothing visible) and row sum of this team's part
+        tmem_st1(x_addr + 2u * team, __float_as_uint((m_raw == -INFINITY) ? -INFINITY : m_use));
+        tmem_st1(x_addr + 2u * team + 1u, __float_as_uint(l_row));
+        tmem_st_wait();
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
-        // P lives in tensor memory and its stores have completed (tcgen05.wait::st), so the arrival orders
-        // nothing; the release form would also wait for this thread's output stores still in flight.
+        // P (and the exchange columns) live in tensor memory and their stores have completed (tcgen05.wait::st), so
+        // the arrivals order nothing; the release form would also wait for this thread's output stores in flight.
         mbar_arrive_cluster_relaxed(p_full_l);
-        if (publishes) mbar_arrive(&sh->xl_full);
+        if (two_parts) mbar_arrive(&sh->xl_full);
       }
-      if (publishes) continue;                 // its O stays in tensor memory until team B has combined it
 
-      // O_B was committed after O_A by the same thread, so for team B this wait covers both.
-      mbar_wait(&sh->o_full[team], ph, ctl, status, kErrWaitMma);
+      // O_B was committed after O_A by the same thread, so in CTA 1 the wait for O_B covers both.
+      mbar_wait(&sh->o_full[two_parts ? 1 : 0], ph, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
       const int clip = pair + (g >> 3) * n_pairs, h = g & 7;
       uint16_t* dst = i < T ? out + (static_cast<long long>(clip) * T + i) * 512 + h * kD : nullptr;
-      uint32_t packed[32];
-      if (combines) {
+      if (two_parts) {
         mbar_wait(&sh->xl_full, ph, ctl, status, kErrWaitConsumer);
-        const float m1 = sh->xs[row][0], l1 = sh->xs[row][1];
-        const float m = fmaxf(m_use, m1);
-        const float a2 = ex2_approx(m_use - m);
-        const float a1 = (m1 == -INFINITY) ? 0.f : ex2_approx(m1 - m);
-        const float inv = 1.f / (a1 * l1 + a2 * l_row);
-        pack_output_row2<VT>(s_addr + kOOff, sa_addr + kOOff, a2 * inv, a1 * inv, packed);
-      } else {
-        pack_output_row<VT>(s_addr + kOOff, 1.f / l_row, packed);
-      }
-      // The score columns are free as soon as O is in registers: the next head's scores do not wait for the
-      // global stores.
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_relaxed(slot_free_l);
-      if (dst != nullptr) {
+        tc_fence_after_sync();
+        uint32_t x4[4];
+        tmem_ld4(x_addr, x4);
+        tmem_ld_wait();
+        const float m_a = __uint_as_float(x4[0]), l_a = __uint_as_float(x4[1]);
+        const float m_b = __uint_as_float(x4[2]), l_b = __uint_as_float(x4[3]);      // finite: a row sees itself
+        const float m = fmaxf(m_a, m_b);
+        const float c_b = ex2_approx(m_b - m);
+        const float c_a = (m_a == -INFINITY) ? 0.f : ex2_approx(m_a - m);
+        const float inv = 1.f / (c_a * l_a + c_b * l_b);
+        uint32_t packed[16];
+        pack_output_half2<VT>(sa_addr + kOOff + 32u * team, sa_addr + kTile + kOOff + 32u * team, c_a * inv, c_b * inv, packed);
+        // The score columns are free as soon as O is in registers: the next head's scores do not wait for the
+        // global stores.
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(slot_free_l);
+        if (dst != nullptr) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          reinterpret_cast<uint4*>(dst)[c] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+          for (int c = 0; c < 2; ++c) st_global_v8(dst + 32 * team + 16 * c, &packed[8 * c]);
+        }
+      } else {
+        uint32_t packed[32];
+        pack_output_row<VT>(s_addr + kOOff, 1.f / l_row, packed);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(slot_free_l);
+        if (dst != nullptr) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) st_global_v8(dst + 16 * c, &packed[8 * c]);
+        }
       }
     }
   }

@@ -234,27 +234,33 @@ def band_attention_prefill(q, k, v, *, window=250, scale=0.125, out=None, status
 
 def attention_prefill(x, w_qkv, cos, sin, *, window=250, scale=0.125, value_dtype=torch.float16,
                       workspace=None, out=None, status=None):
-    """Projection + RoPE + banded attention for a call without cache; returns ``[B,T,512]`` value_dtype: the
-    projection kernel followed by the attention kernel that fits the clip length (``attention_fused`` does the same
-    in one kernel for clips of 129 .. 256 frames, without the q / k / v workspace)."""
+    """Projection + RoPE + banded attention for a call without cache; returns ``[B,T,512]`` value_dtype.  Whole clips
+    of 129 .. 256 frames run as one kernel (no q / k / v in memory: ``workspace`` is not used and not allocated);
+    other lengths as the projection kernel followed by the attention kernel that fits the clip length."""
     lib = _native.load()
     _need(x.dim() == 3, "x must be [B, T, 512]")
     B, T, _ = x.shape
     in_flag = _check_projection_inputs(x, w_qkv)
     bstride = _check_tables(cos, sin, B, T)
-    if workspace is None:
+    one_kernel = 128 < T <= 256
+    if workspace is None and not one_kernel:
         workspace = (torch.empty(x.shape, dtype=torch.bfloat16, device=x.device),
                      torch.empty(x.shape, dtype=torch.bfloat16, device=x.device),
                      torch.empty(x.shape, dtype=value_dtype, device=x.device))
-    q, k, v = workspace
-    _check_frames(q, "q workspace", torch.bfloat16, B * T)
-    _check_frames(k, "k workspace", torch.bfloat16, B * T)
-    _check_frames(v, "v workspace", value_dtype, B * T)
+    ptrs = (None, None, None)
+    if workspace is not None:
+        q, k, v = workspace
+        _check_frames(q, "q workspace", torch.bfloat16, B * T)
+        _check_frames(k, "k workspace", torch.bfloat16, B * T)
+        _check_frames(v, "v workspace", value_dtype, B * T)
+        ptrs = (q.data_ptr(), k.data_ptr(), v.data_ptr())
     if out is None:
         out = torch.empty(x.shape, dtype=value_dtype, device=x.device)
     _check_frames(out, "out", value_dtype, B * T)
+    if B == 0 or T == 0:
+        return out
     rc = lib.fm_attention_prefill_bf16(x.data_ptr(), w_qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), bstride,
-                                       q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, T, window,
+                                       *ptrs, out.data_ptr(), B, T, window,
                                        scale, _VALUE_CODES[value_dtype] | in_flag, _status_ptr(status, x), _stream())
     _native.check(rc, "fm_attention_prefill_bf16")
     return out

@@ -66,8 +66,8 @@ int fm_band_attn_chunk_bf16(const void* q, const void* k, const void* v, void* o
  * 10 s clips): x and W_qkv in, attention output out, the rotated q, k, v never reach memory, so no workspace.
  * Replaces src/fast_mimi/model.py:1897-1914 + :1627-1688 + :1860-1868 for such clips (the reference's own fused
  * front half: src/fast_mimi/_packed_qkv.py:14-131,152-202).  Other T: returns -6 (use fm_attention_prefill_bf16).
- * It moves 2.5 times fewer bytes through HBM than the two-kernel entry point; on B200 it is currently the slower of
- * the two in time, which is why fm_attention_prefill_bf16 does not route to it.  value_dtype as for
+ * It moves 2.5 times fewer bytes through HBM than the two kernels and is the faster of the two forms on B200;
+ * fm_attention_prefill_bf16 routes such clips to it.  value_dtype as for
  * fm_qkv_rope_bf16. */
 int fm_attention_fused_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin, long long cos_bstride,
                             void* out, int B, int T, int window, float scale, int value_dtype, int* status,
@@ -186,9 +186,10 @@ int fm_rvq_to_half(const float* x, void* y, long long rows, void* stream);
 int fm_rvq_decode_f32(const long long* codes, const float* codebooks, float* out, long long rows, int n_layers,
                       int n_codes, int* bad_code, void* stream);
 
-/* fm_qkv_rope_bf16 followed by fm_band_attn_prefill_bf16 on the same stream: the part of
- * MimiAttention.forward between the input and o_proj (src/fast_mimi/model.py:1896-1951) for a call
- * without cache.  q_ws/k_ws/v_ws are caller-provided workspaces of B*T*512 16-bit elements each. */
+/* The part of MimiAttention.forward between the input and o_proj (src/fast_mimi/model.py:1896-1951) for a call
+ * without cache: fm_attention_fused_bf16 for clips of 128 < T <= 256 frames, else fm_qkv_rope_bf16 followed by
+ * fm_band_attn_prefill_bf16 on the same stream.  q_ws/k_ws/v_ws are caller-provided workspaces of B*T*512 16-bit
+ * elements each for the two-kernel form (not touched, and allowed to be null, when 128 < T <= 256). */
 int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos, const float* sin,
                               long long cos_bstride, void* q_ws, void* k_ws, void* v_ws, void* out, int B,
                               int T, int window, float scale, int value_dtype, int* status, void* stream);
