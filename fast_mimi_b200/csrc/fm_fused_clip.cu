@@ -444,12 +444,11 @@ attn_fused_clip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_
       const uint32_t ph = static_cast<uint32_t>(g) & 1u;
       mbar_wait(&sh->s_full, ph, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
-      const float m_raw = tile_row_max(s_addr, vis);
-      const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
-      const float l_row = tile_row_probs<VT>(s_addr, s_addr, vis, scale_log2e, m_use);
+      float m_off;                    // the offset the probabilities were taken against (-inf: nothing visible)
+      const float l_row = tile_row_softmax_online<VT>(s_addr, vis, scale_log2e, m_off);
       if (two_parts) {
-        // scaled row maximum (-inf: nothing visible) and row sum of this team's part
-        tmem_st1(x_addr + 2u * team, __float_as_uint((m_raw == -INFINITY) ? -INFINITY : m_use));
+        // offset and row sum of this team's part
+        tmem_st1(x_addr + 2u * team, __float_as_uint(m_off));
         tmem_st1(x_addr + 2u * team + 1u, __float_as_uint(l_row));
         tmem_st_wait();
       }

@@ -418,6 +418,39 @@ def test_whole_clip_kernels_with_other_windows(T, window):
     fm.check_status()
 
 
+@pytest.mark.parametrize("growth", [0.0, 0.05, 0.1])
+def test_fused_kernel_when_later_keys_score_far_higher(growth):
+    """The one-kernel form exponentiates a row against an offset taken from its first visible keys and raises it only
+    when a later 32-key group exceeds it by 13 binary orders.  Frames whose magnitude grows along the clip make the
+    scores of every row climb from key to key (growth 0.1: by up to about 15 binary orders per 32 keys, so the
+    raise-and-rescale detour runs for most groups; 0.05: a few times per row; 0: never).  q and k are rounded to BF16
+    the same way in both forms, so the check is against the two-kernel form, which subtracts the true row maximum;
+    the mildest case also against the oracle."""
+    import fast_mimi_b200 as fm
+    torch.manual_seed(11)
+    B, T = 2, 250
+    u = torch.randn(512) / 8.0                                    # one direction for all frames: |u_head|^2 about 1
+    amp = 1.0 + growth * torch.arange(T, dtype=torch.float32)
+    x = (amp[None, :, None] * u[None, None, :] + 0.05 * torch.randn(B, T, 512)).bfloat16()
+    eye = torch.eye(512)
+    w = torch.cat([eye, eye, eye * 0.5 + 0.01 * torch.randn(512, 512)]).bfloat16()      # q = k = x
+    cos = torch.ones(1, T, 64); sin = torch.zeros(1, T, 64)        # no rotation: q_i . k_j = a_i a_j |u_head|^2 + noise
+    dev = lambda t: t.cuda()
+    fused = fm.ops.attention_fused(dev(x), dev(w), dev(cos), dev(sin))
+    qd, kd, vd = fm.ops.qkv_rope(dev(x), dev(w), dev(cos), dev(sin))
+    two = fm.ops.band_attention_prefill(qd, kd, vd)
+    fm.check_status()
+    assert torch.isfinite(fused.float()).all()
+    err = O.rel_l2(fused.float().cpu(), two.float().cpu())
+    span = float((qd[0, -1, :64].float() * kd[0, :, :64].float()).sum(-1).max() - (qd[0, -1, :64].float() * kd[0, :, :64].float()).sum(-1).min()) * 0.125 * 1.4427
+    print(f"[growth {growth}] scores of the last row span {span:.0f} binary orders; one-kernel vs two-kernel form: {err:.2e}")
+    assert err < TOL
+    if growth == 0.0:
+        q, k, v = O.qkv_project(x.float(), *w.float().chunk(3, 0))
+        want = O.band_attention(q, k, v).transpose(1, 2).reshape(B, T, 512)
+        assert O.rel_l2(fused.float().cpu(), want) < TOL
+
+
 def test_decode_with_a_different_position_per_stream_across_the_wrap():
     """16 streams at positions (37 s) % 600 + step, stepped over the ring's wrap (249 -> 250 -> 251 for some of
     them), per-stream tables [S, 1, 64] and a device-side stream_pos: every stream's step against the last row of a
