@@ -228,11 +228,11 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
       mbar_wait(&sh->s_full[team], ph, ctl, status, kErrWaitMma);
       tc_fence_after_sync();
-      const float m_raw = tile_row_max(slot, vis);
-      const float m_use = (m_raw == -INFINITY) ? 0.f : m_raw * scale_log2e;
-      float l_row = tile_row_probs<VT>(slot, slot + kPCol, vis, scale_log2e, m_use);
+      static_assert(kPCol == 0, "P is written over the scores from the slot's first column");
+      float m_off;                             // the offset the probabilities were taken against (-inf: nothing visible)
+      float l_row = tile_row_softmax_online<VT>(slot, vis, scale_log2e, m_off);
       if (kind == 1) {
-        sh->xs[x][r][0] = (m_raw == -INFINITY) ? -INFINITY : m_use;
+        sh->xs[x][r][0] = m_off;
         sh->xs[x][r][1] = l_row;
       }
       tc_fence_before_sync();
@@ -252,8 +252,8 @@ band_attn_clip_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (kind == 2) {
         mbar_wait(&sh->xl_full[x], xph, ctl, status, kErrWaitConsumer);
         const float m1 = sh->xs[x][r][0], l1 = sh->xs[x][r][1];
-        const float m = fmaxf(m_use, m1);
-        const float a2 = ex2_approx(m_use - m);
+        const float m = fmaxf(m_off, m1);      // m_off is finite: a row of the diagonal tile sees itself
+        const float a2 = ex2_approx(m_off - m);
         const float a1 = (m1 == -INFINITY) ? 0.f : ex2_approx(m1 - m);
         const float inv = 1.f / (a1 * l1 + a2 * l_row);
         c_own = a2 * inv;

@@ -12,6 +12,7 @@ also sees allocations that bypass PyTorch's caching allocator.
 from __future__ import annotations
 
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -61,6 +62,7 @@ def test_static_workspace_entry_point_matches_the_regular_one_twice():
                                            ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), regular.data_ptr(),
                                            B, T, 250, 0.125, 1, status.data_ptr(), stream)
         assert rc == 0
+        gc.collect()                                   # tensors of earlier tests must not be released mid-measurement
         torch.cuda.synchronize()
         before_torch = torch.cuda.memory_allocated()
         free_before, _ = torch.cuda.mem_get_info()
@@ -70,7 +72,7 @@ def test_static_workspace_entry_point_matches_the_regular_one_twice():
         torch.cuda.synchronize()
         free_after, _ = torch.cuda.mem_get_info()
         assert free_after >= free_before               # no device allocation by any route
-        assert torch.cuda.memory_allocated() == before_torch
+        assert torch.cuda.memory_allocated() <= before_torch
         assert lib.fm_read_status(status.data_ptr(), stream) == 0
         assert torch.isfinite(got.float()).all()
         assert torch.equal(got, want)                  # same kernels on the same inputs: bit-identical
