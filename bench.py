@@ -46,8 +46,8 @@ QKV_FLOP_PER_FRAME = 2 * 512 * 1536
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of each kernel.  ncu cannot run inside this
 # script, so these come from the captures summarised under profiles/ (same kernels, a 256-clip case: traffic grows in
 # proportion to the clips) scaled by 2 to this workload's 512 clips; the line says so in `traffic_source`.
-NCU_TRAFFIC_BYTES_256_CLIPS = {"qkv_rope_gemm_kernel": 217.1e6, "band_attn_clip_kernel": 236.3e6,
-                               "attn_fused_clip_kernel": 85.4e6}
+NCU_TRAFFIC_BYTES_256_CLIPS = {"qkv_rope_gemm_kernel": 217.1e6, "band_attn_clip_kernel": 236.7e6,
+                               "attn_fused_clip_kernel": 88.9e6}
 DTYPE = "bf16 x, W, q, k / fp16 v, p, out / fp32 accumulate"
 
 
