@@ -107,6 +107,7 @@ int fm_attention_prefill_bf16(const void* x, const void* w_qkv, const float* cos
   // the attention kernel that fits it.
   if (T > 128 && T <= 256 && B > 0)
     return fm_attention_fused_bf16(x, w_qkv, cos, sin, cos_bstride, out, B, T, window, scale, value_dtype, status, stream);
+  if (B > 0 && T > 0 && (q_ws == nullptr || k_ws == nullptr || v_ws == nullptr)) return -1;   // this form needs them
   return prefill_two_kernels(x, w_qkv, cos, sin, cos_bstride, q_ws, k_ws, v_ws, out, B, T, window, scale, value_dtype,
                              status, stream);
 }

@@ -418,6 +418,36 @@ def test_whole_clip_kernels_with_other_windows(T, window):
     fm.check_status()
 
 
+def test_cache_free_entry_point_routes_whole_clips_to_one_kernel():
+    """fm_attention_prefill_bf16: clips of 129-256 frames run as one kernel and leave the workspaces alone (null is
+    accepted); other lengths need the workspaces (null is refused before any launch) and fill them."""
+    import fast_mimi_b200 as fm
+    from fast_mimi_b200 import _native
+    lib = _native.load()
+    torch.manual_seed(3)
+    w = (torch.randn(1536, 512) * 0.03).bfloat16().cuda()
+    stream = torch.cuda.current_stream().cuda_stream
+    for T in (250, 100):
+        x = torch.randn(2, T, 512).bfloat16().cuda()
+        cos, sin = (t[None].contiguous().cuda() for t in O.rope_tables(torch.arange(T)))
+        out = torch.zeros(2, T, 512, dtype=torch.float16, device="cuda")
+        rc = lib.fm_attention_prefill_bf16(x.data_ptr(), w.data_ptr(), cos.data_ptr(), sin.data_ptr(), 0, None, None, None,
+                                           out.data_ptr(), 2, T, 250, 0.125, 1, None, stream)
+        torch.cuda.synchronize()
+        if T > 128:
+            assert rc == 0
+            assert torch.equal(out, fm.ops.attention_fused(x, w, cos, sin))
+            ws = [torch.full((2, T, 512), 7.0, dtype=dt, device="cuda") for dt in (torch.bfloat16, torch.bfloat16, torch.float16)]
+            fm.ops.attention_prefill(x, w, cos, sin, workspace=tuple(ws))
+            assert all(bool((t == 7.0).all()) for t in ws)          # untouched
+        else:
+            assert rc == -1 and not out.any()
+            q, k, v = fm.ops.qkv_rope(x, w, cos, sin)
+            want = fm.ops.band_attention_prefill(q, k, v)
+            assert torch.equal(fm.ops.attention_prefill(x, w, cos, sin), want)
+    fm.check_status()
+
+
 @pytest.mark.parametrize("growth", [0.0, 0.05, 0.1])
 def test_fused_kernel_when_later_keys_score_far_higher(growth):
     """The one-kernel form exponentiates a row against an offset taken from its first visible keys and raises it only
