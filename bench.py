@@ -884,8 +884,8 @@ def run_extra_workload(args) -> None:
 
 
 def run_stack(args, dev, peaks, stream, g) -> None:
-    """Whole transformer layers (LayerNorm, projection + RoPE, banded attention, o_proj, LayerNorm, MLP; seven
-    launches per layer) over config 3's batch: 512 clips x 250 frames x 16 layers, FP32 residual stream,
+    """Whole transformer layers (LayerNorm, projection + RoPE + banded attention in one kernel, o_proj, LayerNorm,
+    MLP; six launches per layer, as MimiTransformerLayerB200 issues them) over config 3's batch: 512 clips x 250 frames x 16 layers, FP32 residual stream,
     FP16 tensor-core operands.  One JSON line with per-kernel CUDA-event times and rooflines."""
     from fast_mimi_b200 import ops
     rows = CLIPS * FRAMES
@@ -902,11 +902,10 @@ def run_stack(args, dev, peaks, stream, g) -> None:
     cos, sin = emb.cos()[None].contiguous(), emb.sin()[None].contiguous()
     xa, xb = x0.clone(), torch.empty_like(x0)
     h = torch.empty(x0.shape, dtype=torch.float16, device=dev)
-    q = torch.empty(x0.shape, dtype=torch.bfloat16, device=dev); k = torch.empty_like(q)
-    v = torch.empty_like(h); core = torch.empty_like(h)
+    core = torch.empty_like(h)
     gbuf = torch.empty(CLIPS, FRAMES, 2048, dtype=torch.float16, device=dev)
     status = ops.new_status(dev)
-    names = ["layernorm512 (1)", "qkv_rope_gemm", "band_attn_clip", "linear_gemm o_proj", "layernorm512 (2)",
+    names = ["layernorm512 (1)", "attn_fused_clip (projection + RoPE + attention)", "linear_gemm o_proj", "layernorm512 (2)",
              "linear_gemm fc1+gelu", "linear_gemm fc2"]
 
     def layer(p, x_in, x_mid, x_out, ev=None):
@@ -914,8 +913,7 @@ def run_stack(args, dev, peaks, stream, g) -> None:
             if ev is not None:
                 e = torch.cuda.Event(enable_timing=True); e.record(stream); ev.append(e)
         mark(); ops.layer_norm(x_in, p["ln1w"], p["ln1b"], out=h)
-        mark(); ops.qkv_rope(h, p["qkv"], cos, sin, out=(q, k, v), status=status)
-        mark(); ops.band_attention_prefill(q, k, v, window=WINDOW, scale=0.125, out=core, status=status)
+        mark(); ops.attention_prefill(h, p["qkv"], cos, sin, window=WINDOW, scale=0.125, out=core, status=status)
         mark(); ops.linear(core, p["o"], scale=p["s1"], residual=x_in, out=x_mid, status=status)
         mark(); ops.layer_norm(x_mid, p["ln2w"], p["ln2b"], out=h)
         mark(); ops.linear(h, p["fc1"], activation="gelu", out=gbuf, status=status)
@@ -944,9 +942,9 @@ def run_stack(args, dev, peaks, stream, g) -> None:
     if ops.read_status(status) != 0:
         raise SystemExit("stack: a bounded device wait timed out")
     ms = e0.elapsed_time(e1) / args.steps
-    per = [statistics.mean(ev[i].elapsed_time(ev[i + 1]) for ev in evs) for i in range(7)]
-    flops = [0, 2 * 512 * 1536, 2048 * pairs(FRAMES) / FRAMES, 2 * 512 * 512, 0, 2 * 512 * 2048, 2 * 512 * 2048]
-    nbytes = [2048 + 1024, 1024 + 3072, 4096, 1024 + 2048 + 2048, 2048 + 1024, 1024 + 4096, 4096 + 2048 + 2048]
+    per = [statistics.mean(ev[i].elapsed_time(ev[i + 1]) for ev in evs) for i in range(6)]
+    flops = [0, 2 * 512 * 1536 + 2048 * pairs(FRAMES) / FRAMES, 2 * 512 * 512, 0, 2 * 512 * 2048, 2 * 512 * 2048]
+    nbytes = [2048 + 1024, 1024 + 1024, 1024 + 2048 + 2048, 2048 + 1024, 1024 + 4096, 4096 + 2048 + 2048]
     kernels = []
     for n, t, f, b in zip(names, per, flops, nbytes):
         kernels.append({"kernel": n, "ms": t, "share": t / sum(per), "tflops": rows * f / (t / 1e3) / 1e12,
@@ -957,10 +955,10 @@ def run_stack(args, dev, peaks, stream, g) -> None:
                       "n_gpus": 1, "steps": args.steps, "ms_per_step": ms, "dtype": "fp16 operands, fp32 accumulate and residual stream",
                       "data": "synthetic",
                       "config": {"workload": "whole transformer layers over benchmark config 3's batch", "clips": CLIPS,
-                                 "frames": FRAMES, "layers": LAYERS, "launches_per_layer": 7,
+                                 "frames": FRAMES, "layers": LAYERS, "launches_per_layer": 6,
                                  "l2": "per-layer tensors (0.26-0.52 GB each) exceed the 126 MB L2"},
                       "step_tflops": total_flop / (ms / 1e3) / 1e12, "frac_tensor": total_flop / (ms / 1e3) / 1e12 / peaks["bf16_tflops"],
-                      "gpu_launches": args.steps * LAYERS * 7, "kernels": kernels, "clocks": clocks.summary()}))
+                      "gpu_launches": args.steps * LAYERS * 6, "kernels": kernels, "clocks": clocks.summary()}))
 
 
 def main() -> None:

@@ -5,9 +5,10 @@
 (``self_attn``, ``mlp.fc1``, ``mlp.fc2``, ``input_layernorm``, ``post_attention_layernorm``,
 ``self_attn_layer_scale.scale``, ``mlp_layer_scale.scale``), so state dicts are interchangeable.
 
-The whole layer runs on this package's kernels, seven launches for a call without cache:
+The whole layer runs on this package's kernels, six launches for a call without cache on clips of 129-256 frames
+(seven for other lengths, where projection + RoPE and the attention are two kernels):
 
-    LayerNorm -> QKV projection + RoPE -> banded attention -> o_proj + layer scale + residual
+    LayerNorm -> QKV projection + RoPE + banded attention -> o_proj + layer scale + residual
               -> LayerNorm -> fc1 + GELU -> fc2 + layer scale + residual
 
 The residual stream keeps the caller's dtype (FP32 stays FP32: both residual adds happen in the FP32 epilogue
